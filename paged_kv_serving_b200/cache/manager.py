@@ -35,6 +35,7 @@ class GroupSpec:
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    values: bool = True           # False: one cached vector per position, no value pool
 
 
 @dataclass(frozen=True, slots=True)
@@ -53,12 +54,12 @@ def plan_groups(cache_entries: list[tuple[int, object]]) -> tuple[list[GroupSpec
     states: list[tuple[int, object]] = []
     for number, request in cache_entries:
         if isinstance(request, PagedKVRequest):
-            grouped.setdefault((request.n_kv_heads, request.head_dim, request.window), []).append(number)
+            grouped.setdefault((request.n_kv_heads, request.head_dim, request.window, request.values), []).append(number)
         elif isinstance(request, StateRequest):
             states.append((number, request))
         else:
             raise TypeError(f"unknown cache request {request!r}")
-    groups = [GroupSpec(tuple(entries), kv, hd, window) for (kv, hd, window), entries in grouped.items()]
+    groups = [GroupSpec(tuple(entries), kv, hd, window, values) for (kv, hd, window, values), entries in grouped.items()]
     return groups, states
 
 

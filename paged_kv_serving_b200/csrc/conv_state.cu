@@ -1,0 +1,86 @@
+// A short causal convolution over time on every channel, added to its own input, for a ragged
+// batch of portions of sequences:
+//   out[t] = x[t] + sum_{j < taps} w[:, j] * x[t - taps + 1 + j]        (zeros before position 0)
+// The last taps - 1 inputs of every sequence live in a per-request state [slots, taps - 1, width]
+// (oldest first), so that a sequence can be fed in portions of any size: a token near the start
+// of its portion reads what the portion before left there. Two kernels: the first computes every
+// output of the step and only reads the state, the second (one thread per entry and channel)
+// writes the state the step leaves. Arithmetic is float32; storage float32 or bfloat16.
+#include "common.cuh"
+
+namespace pkv {
+
+constexpr int CONV_MAX_TAPS = 16;
+
+template <typename X>
+__global__ void conv_residual_kernel(const X* __restrict__ x, const float* __restrict__ w, const X* __restrict__ state,
+                                     const int32_t* __restrict__ token_seq, const int32_t* __restrict__ seq_starts,
+                                     const int32_t* __restrict__ state_slots, X* __restrict__ out, int tokens, int width,
+                                     int taps) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * width) return;
+  const int t = (int)(i / width), c = (int)(i - (long long)t * width);
+  const int s = token_seq[t];
+  const int local = t - seq_starts[s];
+  const int slot = state_slots[s];
+  const int tail = taps - 1;
+  const float own = to_float(x[i]);
+  float acc = own * w[(size_t)c * taps + tail];
+  for (int j = 0; j < tail; ++j) {
+    const int src = local - tail + j;              // place inside this portion; negative: before it
+    float v;
+    if (src >= 0) v = to_float(x[(size_t)(t - tail + j) * width + c]);
+    else v = to_float(state[((size_t)slot * tail + (tail + src)) * width + c]);
+    acc = fmaf(w[(size_t)c * taps + j], v, acc);
+  }
+  out[i] = from_float<X>(own + acc);
+}
+
+template <typename X>
+__global__ void conv_state_update_kernel(const X* __restrict__ x, X* __restrict__ state,
+                                         const int32_t* __restrict__ seq_starts, const int32_t* __restrict__ state_slots,
+                                         int seqs, int width, int taps) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)seqs * width) return;
+  const int s = (int)(i / width), c = (int)(i - (long long)s * width);
+  const int start = seq_starts[s], n = seq_starts[s + 1] - start;
+  const int tail = taps - 1;
+  X* mine = state + (size_t)state_slots[s] * tail * width + c;
+  // new[k] = the input at place n - tail + k of this portion, or (before the portion) old[n + k];
+  // ascending k reads old places that have not been written yet
+  for (int k = 0; k < tail; ++k) {
+    const int src = n - tail + k;
+    mine[(size_t)k * width] = src >= 0 ? x[(size_t)(start + src) * width + c] : mine[(size_t)(n + k) * width];
+  }
+}
+
+}  // namespace pkv
+
+using namespace pkv;
+
+PKV_EXPORT int pkv_conv_residual(const void* x, int dtype, const float* w, void* state, const int32_t* token_seq,
+                                 const int32_t* seq_starts, const int32_t* state_slots, void* out, int tokens, int seqs,
+                                 int width, int taps, void* stream) {
+  if (tokens <= 0) return 0;
+  if (width < 1 || taps < 1 || taps > CONV_MAX_TAPS || seqs < 1) return PKV_ERR_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long total = (long long)tokens * width;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  const unsigned state_blocks = (unsigned)(((long long)seqs * width + 255) / 256);
+  if (dtype == PKV_F32) {
+    conv_residual_kernel<float><<<blocks, 256, 0, s>>>((const float*)x, w, (const float*)state, token_seq, seq_starts,
+                                                       state_slots, (float*)out, tokens, width, taps);
+    if (taps > 1)
+      conv_state_update_kernel<float><<<state_blocks, 256, 0, s>>>((const float*)x, (float*)state, seq_starts, state_slots,
+                                                                   seqs, width, taps);
+  } else if (dtype == PKV_BF16) {
+    conv_residual_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)x, w, (const bf16*)state, token_seq, seq_starts,
+                                                      state_slots, (bf16*)out, tokens, width, taps);
+    if (taps > 1)
+      conv_state_update_kernel<bf16><<<state_blocks, 256, 0, s>>>((const bf16*)x, (bf16*)state, seq_starts, state_slots,
+                                                                  seqs, width, taps);
+  } else {
+    return PKV_ERR_DTYPE;
+  }
+  return launch_status();
+}

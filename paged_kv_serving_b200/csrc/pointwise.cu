@@ -1,0 +1,192 @@
+// Element-wise and per-row kernels beside those of elementwise.cu: bias + activation, the
+// residual add that also hands out the stream in the compute type, an activation times a slice
+// of a per-token table, router scores with top-k selection, and the activation of routed experts
+// scaled by the router's weights. Arithmetic is float32 throughout; storage is float32 or bfloat16.
+#include "common.cuh"
+
+namespace pkv {
+
+enum Activation { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_RELU_SQUARED = 3, ACT_SIGMOID = 4 };
+
+__device__ __forceinline__ float activate(float z, int act) {
+  switch (act) {
+    case ACT_GELU_ERF: return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+    case ACT_GELU_TANH: {
+      const float inner = 0.79788456080286535588f * (z + 0.044715f * z * z * z);
+      return 0.5f * z * (1.0f + tanhf(inner));
+    }
+    case ACT_RELU_SQUARED: { const float r = fmaxf(z, 0.0f); return r * r; }
+    case ACT_SIGMOID: return 1.0f / (1.0f + expf(-z));
+    default: return z;
+  }
+}
+
+// out[r, c] = act(x[r, c] + bias[c])
+template <typename X, typename O>
+__global__ void bias_act_kernel(const X* __restrict__ x, const float* __restrict__ bias, O* __restrict__ out,
+                                long long total, int cols, int act) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float z = to_float(x[i]);
+  if (bias) z += bias[i % cols];
+  out[i] = from_float<O>(activate(z, act));
+}
+
+// hidden[r, c] += delta[r, c] + bias[c]; out[r, c] = hidden[r, c] in the type of out
+template <typename D, typename O>
+__global__ void residual_add_kernel(float* __restrict__ hidden, const D* __restrict__ delta,
+                                    const float* __restrict__ bias, O* __restrict__ out, long long total, int cols) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float v = hidden[i];
+  if (delta) v += to_float(delta[i]);
+  if (bias) v += bias[i % cols];
+  hidden[i] = v;
+  if (out) out[i] = from_float<O>(v);
+}
+
+// out[t, j] = act(z[t, j]) * table[ids[t], col0 + j]
+template <typename X>
+__global__ void act_times_table_kernel(const X* __restrict__ z, const X* __restrict__ table, int table_cols,
+                                       int table_rows, const int32_t* __restrict__ ids, int col0, X* __restrict__ out,
+                                       int tokens, int n, int act, const int32_t* __restrict__ fed_back,
+                                       const int32_t* __restrict__ fed_back_at, int* __restrict__ status) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * n) return;
+  const int t = (int)(i / n), j = (int)(i - (long long)t * n);
+  int id = ids[t];
+  if (fed_back_at && fed_back_at[t] >= 0) id = fed_back[fed_back_at[t]];
+  float e = 0.0f;
+  if (id >= 0 && id < table_rows) e = to_float(table[(size_t)id * table_cols + col0 + j]);
+  else if (status) atomicExch(status, PKV_STATUS_BAD_ID);
+  out[i] = from_float<X>(activate(to_float(z[i]), act) * e);
+}
+
+// Router: softmax over the experts' logits of a token, the `top` largest scores kept (the lower
+// index wins a tie), all others zero. weights[t, e] is the score of a chosen expert, not renormalised.
+__global__ void route_top_kernel(const float* __restrict__ logits, int ld, float* __restrict__ weights, int tokens,
+                                 int experts, int top) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= tokens) return;
+  const float* z = logits + (size_t)t * ld;
+  float* w = weights + (size_t)t * experts;
+  float m = -INFINITY;
+  for (int e = 0; e < experts; ++e) m = fmaxf(m, z[e]);
+  float sum = 0.0f;
+  for (int e = 0; e < experts; ++e) sum += expf(z[e] - m);
+  for (int e = 0; e < experts; ++e) w[e] = 0.0f;
+  // pick `top` times the largest logit not picked yet; a picked expert's weight is > 0
+  float last = INFINITY;
+  int last_e = -1;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_e = -1;
+    for (int e = 0; e < experts; ++e) {
+      const float v = z[e];
+      const bool after_last = v < last || (v == last && e > last_e);   // order: score down, index up
+      if (after_last && v > best) { best = v; best_e = e; }
+    }
+    if (best_e < 0) break;
+    w[best_e] = expf(best - m) / sum;
+    last = best;
+    last_e = best_e;
+  }
+}
+
+// up[t, :] holds the up-projections of all routed experts ([experts][ff]) and then of the shared
+// expert ([shared_ff]). out = relu(up)^2 scaled by the router's weight of the column's expert, and
+// for the shared expert by sigmoid(gate[t]).
+template <typename X>
+__global__ void expert_act_kernel(const X* __restrict__ up, int ld, const float* __restrict__ weights,
+                                  const float* __restrict__ gate, int gate_ld, X* __restrict__ out, int tokens,
+                                  int experts, int ff, int shared_ff, int act) {
+  const int cols = experts * ff + shared_ff;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * cols) return;
+  const int t = (int)(i / cols), c = (int)(i - (long long)t * cols);
+  float scale;
+  if (c < experts * ff) scale = weights[(size_t)t * experts + c / ff];
+  else scale = gate ? 1.0f / (1.0f + expf(-gate[(size_t)t * gate_ld])) : 1.0f;
+  float v = 0.0f;
+  if (scale != 0.0f) v = scale * activate(to_float(up[(size_t)t * ld + c]), act);
+  out[(size_t)t * cols + c] = from_float<X>(v);
+}
+
+}  // namespace pkv
+
+using namespace pkv;
+
+static inline unsigned blocks_for(long long total, int threads) { return (unsigned)((total + threads - 1) / threads); }
+
+PKV_EXPORT int pkv_bias_act(const void* x, int x_dtype, const float* bias, void* out, int out_dtype, long long rows,
+                            int cols, int act, void* stream) {
+  const long long total = rows * cols;
+  if (total <= 0) return 0;
+  if (act < 0 || act > 4) return PKV_ERR_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+#define PKV_BA(X, O) bias_act_kernel<X, O><<<blocks_for(total, 256), 256, 0, s>>>((const X*)x, bias, (O*)out, total, cols, act); return launch_status()
+  if (x_dtype == PKV_F32 && out_dtype == PKV_F32) { PKV_BA(float, float); }
+  if (x_dtype == PKV_F32 && out_dtype == PKV_BF16) { PKV_BA(float, bf16); }
+  if (x_dtype == PKV_BF16 && out_dtype == PKV_BF16) { PKV_BA(bf16, bf16); }
+  if (x_dtype == PKV_BF16 && out_dtype == PKV_F32) { PKV_BA(bf16, float); }
+#undef PKV_BA
+  return PKV_ERR_DTYPE;
+}
+
+PKV_EXPORT int pkv_residual_add(float* hidden, const void* delta, int delta_dtype, const float* bias, void* out,
+                                int out_dtype, long long rows, int cols, void* stream) {
+  const long long total = rows * cols;
+  if (total <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+#define PKV_RA(D, O) residual_add_kernel<D, O><<<blocks_for(total, 256), 256, 0, s>>>(hidden, (const D*)delta, bias, (O*)out, total, cols); return launch_status()
+  if (delta_dtype == PKV_F32 && out_dtype == PKV_F32) { PKV_RA(float, float); }
+  if (delta_dtype == PKV_F32 && out_dtype == PKV_BF16) { PKV_RA(float, bf16); }
+  if (delta_dtype == PKV_BF16 && out_dtype == PKV_BF16) { PKV_RA(bf16, bf16); }
+  if (delta_dtype == PKV_BF16 && out_dtype == PKV_F32) { PKV_RA(bf16, float); }
+#undef PKV_RA
+  return PKV_ERR_DTYPE;
+}
+
+PKV_EXPORT int pkv_act_times_table(const void* z, const void* table, int dtype, int table_cols, int table_rows,
+                                   const int32_t* ids, int col0, void* out, int tokens, int n, int act,
+                                   const int32_t* fed_back, const int32_t* fed_back_at, int* status, void* stream) {
+  const long long total = (long long)tokens * n;
+  if (total <= 0) return 0;
+  if (col0 < 0 || col0 + n > table_cols || act < 0 || act > 4) return PKV_ERR_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PKV_F32) {
+    act_times_table_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)z, (const float*)table, table_cols,
+        table_rows, ids, col0, (float*)out, tokens, n, act, fed_back, fed_back_at, status);
+  } else if (dtype == PKV_BF16) {
+    act_times_table_kernel<bf16><<<blocks_for(total, 256), 256, 0, s>>>((const bf16*)z, (const bf16*)table, table_cols,
+        table_rows, ids, col0, (bf16*)out, tokens, n, act, fed_back, fed_back_at, status);
+  } else {
+    return PKV_ERR_DTYPE;
+  }
+  return launch_status();
+}
+
+PKV_EXPORT int pkv_route_top(const float* logits, int ld, float* weights, int tokens, int experts, int top, void* stream) {
+  if (tokens <= 0) return 0;
+  if (experts < 1 || top < 1 || top > experts || ld < experts) return PKV_ERR_SIZE;
+  route_top_kernel<<<blocks_for(tokens, 128), 128, 0, (cudaStream_t)stream>>>(logits, ld, weights, tokens, experts, top);
+  return launch_status();
+}
+
+PKV_EXPORT int pkv_expert_act(const void* up, int dtype, int ld, const float* weights, const float* gate, int gate_ld,
+                              void* out, int tokens, int experts, int ff, int shared_ff, int act, void* stream) {
+  const long long total = (long long)tokens * ((long long)experts * ff + shared_ff);
+  if (total <= 0) return 0;
+  if (experts < 0 || ff < 0 || shared_ff < 0 || act < 0 || act > 4) return PKV_ERR_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PKV_F32) {
+    expert_act_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)up, ld, weights, gate, gate_ld,
+                                                                    (float*)out, tokens, experts, ff, shared_ff, act);
+  } else if (dtype == PKV_BF16) {
+    expert_act_kernel<bf16><<<blocks_for(total, 256), 256, 0, s>>>((const bf16*)up, ld, weights, gate, gate_ld,
+                                                                   (bf16*)out, tokens, experts, ff, shared_ff, act);
+  } else {
+    return PKV_ERR_DTYPE;
+  }
+  return launch_status();
+}

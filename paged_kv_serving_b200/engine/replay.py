@@ -119,13 +119,15 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--max-tokens", required=True, type=int,
                         help="most tokens live requests hold at any time (each rounded up to 64)")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per page of the cache (default 16)")
+    parser.add_argument("--max-live", type=int, default=4,
+                        help="requests that may be live at once: state slots of models that keep a state (default 4)")
     args = parser.parse_args(argv)
 
     print("[trace_run] loading the model", file=sys.stderr, flush=True)
     from paged_kv_serving_b200.models.decoder import DecoderModel
 
     model = DecoderModel.from_folder(args.model, dtype=args.dtype, device="cuda")
-    session = ReplaySession(model, max_tokens=args.max_tokens, block_size=args.block_size)
+    session = ReplaySession(model, max_tokens=args.max_tokens, block_size=args.block_size, max_live=args.max_live)
     args.out.mkdir(parents=True, exist_ok=True)
     print("[trace_run] ready", file=sys.stderr, flush=True)
     for line in sys.stdin:

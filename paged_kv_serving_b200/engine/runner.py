@@ -34,8 +34,9 @@ __all__ = ["CacheStorage", "ModelRunner", "StepResult"]
 
 class CacheStorage:
     """Device memory of the cache: per page group one key pool and one value pool shaped
-    ``[layers of the group, pages, kv heads, page_size, head_dim]``, and per state entry a
-    tensor ``[slots, *shape]``."""
+    ``[layers of the group, pages, kv heads, page_size, head_dim]`` (no value pool for a group
+    without values), and per state entry a tensor ``[slots + 1, *shape]``: the last slot belongs to
+    no request, the stand-in entries that pad a captured step to its size class use it."""
 
     def __init__(self, groups: list[GroupSpec], state_entries: list, *, num_blocks: int, block_size: int,
                  dtype: torch.dtype, device: torch.device, num_state_slots: int) -> None:
@@ -43,30 +44,34 @@ class CacheStorage:
         self.num_blocks = num_blocks
         self.block_size = block_size
         self.k_pools: list[torch.Tensor] = []
-        self.v_pools: list[torch.Tensor] = []
+        self.v_pools: list[torch.Tensor | None] = []
         self.location: dict[int, tuple[int, int]] = {}
         for g, spec in enumerate(groups):
             shape = (len(spec.entries), num_blocks, spec.n_kv_heads, block_size, spec.head_dim)
             self.k_pools.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=device) if spec.values else None)
             for index, entry in enumerate(spec.entries):
                 self.location[entry] = (g, index)
         self.states: list[torch.Tensor] = []
         self.state_index: dict[int, int] = {}
         for entry, request in state_entries:
-            state_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[request.dtype]
+            state_dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16, "compute": dtype}[request.dtype]
             self.state_index[entry] = len(self.states)
-            self.states.append(torch.zeros((max(1, num_state_slots), *request.shape), dtype=state_dtype, device=device))
+            self.states.append(torch.zeros((max(1, num_state_slots) + 1, *request.shape), dtype=state_dtype, device=device))
+
+    def _pools(self) -> list[torch.Tensor]:
+        return [t for t in (*self.k_pools, *self.v_pools) if t is not None]
 
     @property
     def cache_bytes(self) -> int:
-        pools = sum(t.numel() * t.element_size() for t in (*self.k_pools, *self.v_pools))
+        pools = sum(t.numel() * t.element_size() for t in self._pools())
         return pools + sum(t.numel() * t.element_size() for t in self.states)
 
     def copy_page(self, group: int, source: int, destination: int) -> None:
         if source == destination:
             raise ValueError("a page is never copied onto itself")
-        ops.copy_page(self.k_pools[group], self.v_pools[group], source, destination)
+        values = self.v_pools[group]
+        ops.copy_page(self.k_pools[group], values if values is not None else self.k_pools[group], source, destination)
 
     def copy_state(self, source_slot: int, destination_slot: int) -> None:
         for state in self.states:
@@ -79,17 +84,19 @@ class CacheStorage:
                 state.index_fill_(0, index, 0)
 
     def reset(self) -> None:
-        for tensor in (*self.k_pools, *self.v_pools, *self.states):
+        for tensor in (*self._pools(), *self.states):
             tensor.zero_()
 
     def fill(self, value: float) -> None:
         """Overwrite every page with ``value`` (tests poison the pool with it)."""
-        for tensor in (*self.k_pools, *self.v_pools):
+        for tensor in self._pools():
             tensor.fill_(value)
 
     def page_fingerprint(self, group: int, page: int) -> bytes:
         digest = hashlib.blake2b(digest_size=16)
         for pool in (self.k_pools[group], self.v_pools[group]):
+            if pool is None:
+                continue
             digest.update(pool[:, page].contiguous().view(torch.uint8).cpu().numpy().tobytes())
         return digest.digest()
 
@@ -137,6 +144,14 @@ class ModelRunner:
                 self.bindings.append(CacheBinding(call.cache, group=g, index=index, write=call.write))
             else:
                 self.bindings.append(CacheBinding(call.cache, state=self.storage.state_index[call.cache], write=call.write))
+            if call.extra:
+                extra = {name: self.storage.state_index[number] for name, number in call.extra}
+                binding = self.bindings[-1]
+                self.bindings[-1] = CacheBinding(call.cache if binding is None else binding.entry,
+                                                 group=None if binding is None else binding.group,
+                                                 index=None if binding is None else binding.index,
+                                                 state=None if binding is None else binding.state,
+                                                 write=call.write, extra=extra)
         self._status = ops.status_word(model.device)
         # Where a sampler leaves the ids of a step (and, behind them, the status word) so that the
         # next step's embedding lookup can read a decoded token without a trip through the host.
@@ -224,7 +239,8 @@ class ModelRunner:
         id lies (the entry's own ``token_ids`` is then a stand-in)."""
         entries = batch.entries
         if pad_to is not None and len(entries) < pad_to:
-            filler = BatchEntry("", (0,), 0, tuple((NULL_PAGE,) for _ in self.groups), (0,), 0)
+            # (a stand-in's state goes to the spare slot behind those of the requests)
+            filler = BatchEntry("", (0,), 0, tuple((NULL_PAGE,) for _ in self.groups), (0,), self.num_state_slots)
             entries = entries + (filler,) * (pad_to - len(entries))
         lens = [e.num_tokens for e in entries]
         total = sum(lens)
@@ -242,6 +258,7 @@ class ModelRunner:
         arena.add(StepContext.FIRST_POS, first)
         arena.add(StepContext.CONTEXT_LENS, first + np.asarray(lens))
         arena.add(StepContext.STATE_SLOTS, [e.state_slot if e.state_slot is not None else 0 for e in entries])
+        arena.add(StepContext.TOKEN_SEQ, seq_of_token)
         rows: list[tuple[str, int]] = []
         row_index: list[int] = []
         for e, start in zip(entries, starts[:-1]):

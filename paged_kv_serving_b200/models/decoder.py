@@ -41,6 +41,8 @@ class DecoderModel:
         layout = registry.architecture(config.architecture).layout(config)
         model = cls(config, layout, dtype, torch.device(device))
         specs = layout.tensor_specs()
+        if layout.optional_names:
+            tensors = {name: t for name, t in tensors.items() if name in specs or name not in layout.optional_names}
         loader.check_tensors(specs, tensors)
         placed = {name: loader.place(tensors[name], spec, model.dtype, model.device) for name, spec in specs.items()}
         loader.check_finite(placed)      # one pass on the device, after the cast to the compute type

@@ -19,6 +19,9 @@ class LayerCall:
     layer: int
     cache: int | None = None
     write: bool = True
+    #: ``(name, cache entry number)`` of the call's further states (``Part.state_requests``);
+    #: ``resolved_order`` fills it in, a fresh entry per call and name.
+    extra: tuple = ()
 
 
 @dataclass(slots=True)
@@ -46,6 +49,8 @@ class ModelLayout:
     #: another kind of embedding or head passes its own parts and names their tensors in ``names``.
     embedding: Part | None = None
     head: Part | None = None
+    #: Tensors a model folder may hold although the layout has no use for them (they are not loaded).
+    optional_names: set = field(default_factory=set)
 
     def __post_init__(self) -> None:
         from paged_kv_serving_b200.parts.io import LinearHead, TokenEmbedding
@@ -88,6 +93,10 @@ class ModelLayout:
             else:
                 seen[call.cache] = request
             next_free = max(next_free, call.cache + 1)
+        for call in self.resolved_order():
+            requests = self.blocks[call.layer].state_requests()
+            for name, number in call.extra:
+                seen[number] = requests[name]
         return sorted(seen.items())
 
     def resolved_order(self) -> list[LayerCall]:
@@ -99,10 +108,16 @@ class ModelLayout:
             if not 0 <= call.layer < len(self.blocks):
                 raise ValueError(f"layer call names layer {call.layer}, the model has {len(self.blocks)}")
             if call.cache is None and self.blocks[call.layer].cache_request() is not None:
-                out.append(LayerCall(call.layer, next_free, call.write))
+                call = LayerCall(call.layer, next_free, call.write)
                 next_free += 1
-            else:
-                out.append(call)
+            out.append(call)
+        # the further states of every call come after all primary entries, one entry per call and name
+        for i, call in enumerate(out):
+            names = sorted(self.blocks[call.layer].state_requests())
+            if names and not call.extra:
+                out[i] = LayerCall(call.layer, call.cache, call.write,
+                                   tuple((name, next_free + k) for k, name in enumerate(names)))
+                next_free += len(names)
         return out
 
 

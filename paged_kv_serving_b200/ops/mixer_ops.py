@@ -1,0 +1,228 @@
+"""Bindings of the kernels in ``csrc/pointwise.cu``, ``csrc/conv_state.cu``, ``csrc/mlstm.cu`` and
+``csrc/latent_attention.cu``: what mixers with a state of their own, a cached latent, routed
+experts and per-token side inputs need beside the kernels bound in ``ops/__init__.py``.
+The same conventions hold: CUDA tensors only, launches on torch's current stream, a refused
+argument raises ``ValueError``, nothing falls back to a library or to the CPU.
+"""
+
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from paged_kv_serving_b200 import ops
+from paged_kv_serving_b200.ops import _check, _fn, _need, _ptr, _stream, dtype_code
+from paged_kv_serving_b200.ops.arena import empty as _empty
+
+__all__ = ["ACTIVATIONS", "act_times_table", "bias_act", "conv_residual", "expert_act", "latent_attention",
+           "latent_prepare", "latent_rows_per_block", "mlstm", "residual_add", "route_top"]
+
+#: activation names of ``bias_act`` / ``act_times_table`` / ``expert_act``
+ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "relu_squared": 3, "sigmoid": 4}
+
+
+def bias_act(x: torch.Tensor, bias: torch.Tensor | None, act: str, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``act(x + bias)`` for ``x [rows, cols]`` and a float32 ``bias [cols]`` (or none)."""
+    _need(x, None, "x")
+    rows, cols = x.shape
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != cols:
+            raise ValueError(f"bias has {bias.numel()} elements for {cols} columns")
+    out = _empty((rows, cols), out_dtype or x.dtype, x.device)
+    fn = _fn("pointwise", "pkv_bias_act", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), dtype_code(x.dtype), _ptr(bias), _ptr(out), dtype_code(out.dtype), rows, cols, ACTIVATIONS[act],
+              _stream()), "bias_act")
+    return out
+
+
+def residual_add(hidden: torch.Tensor, delta: torch.Tensor | None, bias: torch.Tensor | None = None,
+                 out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+    """``hidden += delta + bias`` in place (float32 stream) and, with ``out_dtype``, the stream in
+    that type (what a product that reads the stream itself, not a norm of it, takes)."""
+    _need(hidden, torch.float32, "hidden")
+    rows, cols = hidden.shape
+    if delta is not None:
+        _need(delta, None, "delta")
+        if delta.shape != hidden.shape:
+            raise ValueError("delta and hidden differ in shape")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != cols:
+            raise ValueError("bias does not fit the stream's width")
+    out = _empty((rows, cols), out_dtype, hidden.device) if out_dtype is not None else None
+    fn = _fn("pointwise", "pkv_residual_add", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p])
+    _check(fn(_ptr(hidden), _ptr(delta), dtype_code(delta.dtype) if delta is not None else 0, _ptr(bias), _ptr(out),
+              dtype_code(out_dtype) if out_dtype is not None else 0, rows, cols, _stream()), "residual_add")
+    return out
+
+
+def act_times_table(z: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0: int, act: str, status: torch.Tensor,
+                    fed_back: torch.Tensor | None = None, fed_back_at: torch.Tensor | None = None) -> torch.Tensor:
+    """``act(z[t, j]) * table[ids[t], col0 + j]`` for ``z [tokens, n]``; ids as in ``embedding_gather``."""
+    _need(z, None, "z"); _need(table, z.dtype, "table"); _need(ids, torch.int32, "ids")
+    tokens, n = z.shape
+    out = _empty((tokens, n), z.dtype, z.device)
+    fn = _fn("pointwise", "pkv_act_times_table",
+             [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+              c_void_p, c_void_p])
+    _check(fn(_ptr(z), _ptr(table), dtype_code(z.dtype), table.shape[1], table.shape[0], _ptr(ids), int(col0), _ptr(out),
+              tokens, n, ACTIVATIONS[act], _ptr(fed_back), _ptr(fed_back_at), _ptr(status), _stream()), "act_times_table")
+    return out
+
+
+def route_top(logits: torch.Tensor, experts: int, top: int) -> torch.Tensor:
+    """Router weights ``[tokens, experts]`` (float32): the softmax score of each of a token's
+    ``top`` best experts, zero elsewhere. ``logits [tokens, >= experts]`` float32 (further columns
+    are ignored)."""
+    _need(logits, torch.float32, "logits")
+    tokens, ld = logits.shape
+    out = _empty((tokens, experts), torch.float32, logits.device)
+    fn = _fn("pointwise", "pkv_route_top", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(logits), ld, _ptr(out), tokens, experts, top, _stream()), "route_top")
+    return out
+
+
+def expert_act(up: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor | None, experts: int, ff: int, shared_ff: int,
+               act: str) -> torch.Tensor:
+    """``weights[t, e] * act(up[t, e * ff + j])`` for the routed experts' columns and
+    ``sigmoid(gate[t]) * act(up)`` for the ``shared_ff`` columns behind them; ``gate`` is a float32
+    column view ``[tokens]`` (any stride) or none. ``up`` may have further (padding) columns."""
+    _need(up, None, "up"); _need(weights, torch.float32, "weights")
+    tokens, ld = up.shape
+    cols = experts * ff + shared_ff
+    if ld < cols or weights.shape != (tokens, experts):
+        raise ValueError("expert_act: sizes do not fit")
+    gate_ld = 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.dim() != 1 or gate.shape[0] != tokens:
+            raise ValueError("gate must be float32 [tokens]")
+        gate_ld = gate.stride(0)
+    out = _empty((tokens, cols), up.dtype, up.device)
+    fn = _fn("pointwise", "pkv_expert_act",
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(up), dtype_code(up.dtype), ld, _ptr(weights), _ptr(gate), gate_ld, _ptr(out), tokens, experts, ff,
+              shared_ff, ACTIVATIONS[act], _stream()), "expert_act")
+    return out
+
+
+def conv_residual(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, token_seq: torch.Tensor,
+                  seq_starts: torch.Tensor, state_slots: torch.Tensor) -> torch.Tensor:
+    """``x + causal_conv(x)`` per channel for a ragged batch, ``weight [width, taps]`` float32 with
+    tap ``taps - 1`` on the token itself; ``state [slots, taps - 1, width]`` (type of ``x``) holds
+    every request's last inputs and is brought up to date."""
+    _need(x, None, "x"); _need(weight, torch.float32, "weight")
+    tokens, width = x.shape
+    taps = weight.shape[1]
+    if weight.shape[0] != width:
+        raise ValueError("conv weight does not fit the width")
+    if taps > 1:
+        _need(state, x.dtype, "state")
+        if state.shape[1:] != (taps - 1, width):
+            raise ValueError("conv state must be [slots, taps - 1, width]")
+    seqs = seq_starts.numel() - 1
+    out = _empty((tokens, width), x.dtype, x.device)
+    fn = _fn("conv_state", "pkv_conv_residual",
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), dtype_code(x.dtype), _ptr(weight), _ptr(state), _ptr(token_seq), _ptr(seq_starts), _ptr(state_slots),
+              _ptr(out), tokens, seqs, width, taps, _stream()), "conv_residual")
+    ops.LAUNCHES["count"] += 1 if taps > 1 else 0
+    return out
+
+
+def mlstm(proj: torch.Tensor, offsets: dict[str, int], i_bias: torch.Tensor, f_bias: torch.Tensor, norm_weight: torch.Tensor,
+          cap: float, q_scale: float, eps: float, s_state: torch.Tensor, n_state: torch.Tensor, m_state: torch.Tensor,
+          seq_starts: torch.Tensor, state_slots: torch.Tensor, heads: int, dim: int, vdim: int,
+          out_dtype: torch.dtype) -> torch.Tensor:
+    """The mLSTM recurrence over a ragged batch. ``proj`` float32 ``[tokens, ld]`` holds the
+    projections q, k ``[heads, dim]``, v, g ``[heads, vdim]`` and the two gates' pre-activations
+    ``[heads]`` at ``offsets`` ("q", "k", "v", "g", "i", "f"). States (float32): ``s_state [slots,
+    heads, dim, vdim]``, ``n_state [slots, heads, dim]``, ``m_state [slots, heads]``. Returns the
+    heads' outputs after their unit norm, the norm's weight and the output gate, ``[tokens, heads * vdim]``."""
+    _need(proj, torch.float32, "proj")
+    for name, t in (("s_state", s_state), ("n_state", n_state), ("m_state", m_state), ("i_bias", i_bias), ("f_bias", f_bias),
+                    ("norm_weight", norm_weight)):
+        _need(t, torch.float32, name)
+    tokens, ld = proj.shape
+    if s_state.shape[1:] != (heads, dim, vdim) or n_state.shape[1:] != (heads, dim) or m_state.shape[1:] != (heads,):
+        raise ValueError("mlstm: the states do not fit heads, dim and vdim")
+    if norm_weight.numel() != heads * vdim or i_bias.numel() != heads or f_bias.numel() != heads:
+        raise ValueError("mlstm: a vector does not fit the head count")
+    seqs = seq_starts.numel() - 1
+    coef = _empty((tokens, heads, 4), torch.float32, proj.device)
+    o = _empty((tokens, heads * vdim), torch.float32, proj.device)
+    out = _empty((tokens, heads * vdim), out_dtype, proj.device)
+    fn = _fn("mlstm", "pkv_mlstm",
+             [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float,
+              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+              c_int, c_void_p])
+    _check(fn(_ptr(proj), ld, offsets["q"], offsets["k"], offsets["v"], offsets["g"], offsets["i"], offsets["f"],
+              _ptr(i_bias), _ptr(f_bias), _ptr(norm_weight), float(cap), float(q_scale), float(eps), _ptr(s_state),
+              _ptr(n_state), _ptr(m_state), _ptr(seq_starts), _ptr(state_slots), _ptr(coef), _ptr(o), _ptr(out),
+              dtype_code(out_dtype), tokens, seqs, heads, dim, vdim, _stream()), "mlstm")
+    ops.LAUNCHES["count"] += 2
+    return out
+
+
+def latent_rows_per_block() -> int:
+    fn = ops.library("latent_attention").pkv_latent_rows_per_block
+    fn.restype = c_int
+    return int(fn())
+
+
+def latent_prepare(fused: torch.Tensor, q_off: int, q_rank: int, kv_off: int, rank: int, rot: int, rot_dims: int,
+                   q_weight: torch.Tensor, kv_weight: torch.Tensor, freq: torch.Tensor, eps: float, positions: torch.Tensor,
+                   slots: torch.Tensor | None, pool: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    """From the fused down-projections ``fused`` (float32 ``[tokens, ld]``): the RMS-normalised
+    query latent ``[tokens, q_rank]`` (returned, in the pool's type), and the cache row
+    ``[normalised latent | rotated key part]`` written at ``slots`` (int32 per token, negative or
+    ``None``: nothing is written) of ``pool [pages, 1, page_size, rank + rot]``."""
+    _need(fused, torch.float32, "fused"); _need(pool, None, "pool"); _need(freq, torch.float32, "freq")
+    _need(q_weight, torch.float32, "q_weight"); _need(kv_weight, torch.float32, "kv_weight")
+    tokens, ld = fused.shape
+    if pool.shape[-1] != rank + rot:
+        raise ValueError("the pool's rows must hold rank + rot values")
+    pool_rows = pool.numel() // (rank + rot)
+    c_q = _empty((tokens, q_rank), pool.dtype, fused.device)
+    fn = _fn("latent_attention", "pkv_latent_prepare",
+             [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+              c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(fused), ld, q_off, q_rank, kv_off, rank, rot, rot_dims, _ptr(q_weight), _ptr(kv_weight), _ptr(freq),
+              float(eps), _ptr(positions), _ptr(slots), _ptr(c_q), _ptr(pool), dtype_code(pool.dtype), pool_rows, tokens,
+              _ptr(status), _stream()), "latent_prepare")
+    return c_q
+
+
+def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_rot_offset: int, q_head_stride: int, pool: torch.Tensor,
+                     block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor, work_seq: torch.Tensor,
+                     work_row0: torch.Tensor, freq: torch.Tensor, gate: torch.Tensor | None, heads: int, rank: int, rot: int,
+                     rot_dims: int, page_size: int, window: int, scale: float, status: torch.Tensor,
+                     n_work: int | None = None) -> torch.Tensor:
+    """Causal attention of absorbed queries over the cached latent. ``q_lat [heads, tokens, rank]``
+    (float32, or the type of ``q``); the rotated part of head ``h`` of token ``t`` is read (and
+    rotated) from ``q[t, h * q_head_stride + q_rot_offset :][:rot]``; ``gate`` float32 ``[tokens, >=
+    heads]`` (a view with a row stride) multiplies the result by its sigmoid. Returns ``[heads,
+    tokens, rank]`` in the type of ``q``: per head the softmax-weighted sum of the latents."""
+    _need(q_lat, None, "q_lat"); _need(q, None, "q"); _need(pool, q.dtype, "pool")
+    tokens = q.shape[0]
+    if q_lat.shape != (heads, tokens, rank):
+        raise ValueError("q_lat must be [heads, tokens, rank]")
+    gate_ld = 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.stride(1) != 1:
+            raise ValueError("gate must be a float32 [tokens, heads] view with unit inner stride")
+        gate_ld = gate.stride(0)
+    out = _empty((heads, tokens, rank), q.dtype, q.device)
+    num_pages = pool.numel() // (page_size * (rank + rot))
+    fn = _fn("latent_attention", "pkv_latent_attention",
+             [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+              c_int, c_void_p, c_void_p])
+    q_rot = q.view(-1)[q_rot_offset:]
+    _check(fn(_ptr(q_lat), dtype_code(q_lat.dtype), c_void_p(q_rot.data_ptr()), q.stride(0), q_head_stride, _ptr(out),
+              dtype_code(q.dtype), _ptr(pool), dtype_code(pool.dtype), _ptr(block_table), block_table.shape[1],
+              _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), _ptr(work_row0), work_seq.numel() if n_work is None else int(n_work), _ptr(freq), _ptr(gate),
+              gate_ld, tokens, heads, rank, rot, rot_dims, page_size, int(window), float(scale), num_pages, _ptr(status),
+              _stream()), "latent_attention")
+    return out

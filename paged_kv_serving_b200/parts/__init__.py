@@ -5,14 +5,19 @@ from paged_kv_serving_b200.parts.attention import PagedAttention
 from paged_kv_serving_b200.parts.base import (
     Block, CacheBinding, GroupView, IntArena, Normed, PagedKVRequest, ParamSpec, Part, StateRequest, StepContext,
 )
-from paged_kv_serving_b200.parts.block import PreNormBlock
-from paged_kv_serving_b200.parts.feed_forward import SwiGLU
+from paged_kv_serving_b200.parts.block import ConvSideBlock, PreNormBlock
+from paged_kv_serving_b200.parts.conv import ResidualCausalConv
+from paged_kv_serving_b200.parts.feed_forward import BiasedDense, RoutedExperts, SwiGLU
 from paged_kv_serving_b200.parts.io import LinearHead, TokenEmbedding
-from paged_kv_serving_b200.parts.norms import RMSNorm
+from paged_kv_serving_b200.parts.latent_attention import LatentAttention
+from paged_kv_serving_b200.parts.mlstm import MLSTM
+from paged_kv_serving_b200.parts.norms import RMSNorm, ScalarRMSNorm
 from paged_kv_serving_b200.parts.position import NoPositionEncoding, PositionEncoding, RotaryEncoding
+from paged_kv_serving_b200.parts.token_side import TokenSideInput, TokenSideTable
 
 __all__ = [
-    "Block", "CacheBinding", "GroupView", "IntArena", "LinearHead", "NoPositionEncoding", "Normed", "PagedAttention",
-    "PagedKVRequest", "ParamSpec", "Part", "PositionEncoding", "PreNormBlock", "RMSNorm", "RotaryEncoding",
-    "StateRequest", "StepContext", "SwiGLU", "TokenEmbedding",
+    "BiasedDense", "Block", "CacheBinding", "ConvSideBlock", "GroupView", "IntArena", "LatentAttention", "LinearHead", "MLSTM",
+    "NoPositionEncoding", "Normed", "PagedAttention", "PagedKVRequest", "ParamSpec", "Part", "PositionEncoding",
+    "PreNormBlock", "RMSNorm", "ResidualCausalConv", "RotaryEncoding", "RoutedExperts", "ScalarRMSNorm", "StateRequest",
+    "StepContext", "SwiGLU", "TokenEmbedding", "TokenSideInput", "TokenSideTable",
 ]

@@ -43,12 +43,16 @@ class PagedKVRequest:
     n_kv_heads: int
     head_dim: int
     window: int | None = None
+    #: False for a mixer that caches one vector per position and reads its values out of it
+    #: (a latent): the group then has no value pool, and ``GroupView.v_pool`` is ``None``.
+    values: bool = True
 
 
 @dataclass(frozen=True, slots=True)
 class StateRequest:
     """A fixed-size state per running request, e.g. ``shape=(heads, dim)``; zeroed when a request
-    (re)starts from position zero."""
+    (re)starts from position zero. ``dtype`` is "float32", "bfloat16" or "compute" (the engine's
+    compute type: what a state that holds activations wants)."""
 
     shape: tuple[int, ...]
     dtype: str = "float32"
@@ -72,6 +76,13 @@ class Part:
 
     def cache_request(self) -> PagedKVRequest | StateRequest | None:
         return None
+
+    def state_requests(self) -> dict[str, StateRequest]:
+        """Further fixed-size states of a layer call, by name, beside what ``cache_request`` asks
+        for: a mixer with several state tensors, or a block whose parts each keep one (a short
+        convolution's last inputs next to the mixer's keys). Every layer call gets its own; the
+        call finds them as ``ctx.states[binding.extra[name]]``, shaped ``[slots, *shape]``."""
+        return {}
 
     #: True when ``forward`` only launches work on the current stream (no host reads of device
     #: data, no host-dependent control flow), so that a step may be captured in a CUDA graph.
@@ -234,6 +245,8 @@ class CacheBinding:
     index: int | None = None
     state: int | None = None
     write: bool = True
+    #: name -> index into ``StepContext.states`` of the call's further states (``Part.state_requests``)
+    extra: dict = field(default_factory=dict, hash=False, compare=False)
 
 
 @dataclass(slots=True)
@@ -241,7 +254,7 @@ class GroupView:
     """One page group as a step sees it."""
 
     k_pool: torch.Tensor          # [layers of the group, pages, KV, page_size, hd]
-    v_pool: torch.Tensor
+    v_pool: torch.Tensor | None   # None for a group without values (``PagedKVRequest.values``)
     page_size: int
     window: int | None
     table_name: str               # arena names of this group's arrays
@@ -278,6 +291,7 @@ class StepContext:
     FIRST_POS = "first_pos"
     CONTEXT_LENS = "context_lens"
     STATE_SLOTS = "state_slots"
+    TOKEN_SEQ = "token_seq"             # per token: the number of its entry in the step
     LOGITS_ROWS = "logits_rows"
     TOKEN_FEEDBACK = "token_feedback"   # per token: -1, or the place of its id in the sampler's output buffer
 

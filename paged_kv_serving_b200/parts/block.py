@@ -8,7 +8,7 @@ from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.parts.base import Block, CacheBinding, Normed, Part, StepContext
 
-__all__ = ["PreNormBlock"]
+__all__ = ["ConvSideBlock", "PreNormBlock"]
 
 
 @register_part("block", "prenorm_residual")
@@ -83,3 +83,70 @@ class PreNormBlock(Block):
                 normed, ctx, finish=lambda x, w: follow(hidden, x, w, ctx.dtype, chain=chain))
             return Normed(values, next_norm)
         return self.feed_forward.forward(normed, ctx)
+
+
+@register_part("block", "prenorm_conv_side")
+class ConvSideBlock(Block):
+    """Pre-norm residual arrangement with two optional additions:
+
+    ``h = norm1(x)``; with ``input_conv``, ``h <- h + conv(h)`` (a short causal convolution whose
+    tail is state of the layer call); ``x += mixer(h)``; with a feed-forward, ``x += ff(norm2(x))``;
+    with ``side``, ``x += side(x, tokens)`` (a per-token input computed from the stream itself).
+
+    The mixer is called as ``forward(h, ctx, binding)``, the feed-forward as ``forward(h, ctx)``.
+    Updates travel as pending tensors as ``Block`` describes; this block applies no norm for its
+    successor and accepts none from its predecessor (``first_norm`` is ``None``).
+    """
+
+    def __init__(self, mixer_norm: Part, mixer: Part, ff_norm: Part | None = None, feed_forward: Part | None = None,
+                 input_conv: Part | None = None, side: Part | None = None) -> None:
+        if (ff_norm is None) != (feed_forward is None):
+            raise ValueError("a feed-forward and its norm go together")
+        self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward = mixer_norm, mixer, ff_norm, feed_forward
+        self.input_conv, self.side = input_conv, side
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(child.graph_safe for child in self.sub_parts().values())
+
+    def sub_parts(self) -> dict[str, Part]:
+        parts = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ff_norm": self.ff_norm,
+                 "feed_forward": self.feed_forward, "input_conv": self.input_conv, "side": self.side}
+        return {name: part for name, part in parts.items() if part is not None}
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def state_requests(self):
+        requests = {}
+        for child in self.sub_parts().values():
+            for name, request in child.state_requests().items():
+                if name in requests:
+                    raise ValueError(f"two parts of one block ask for a state named {name!r}")
+                requests[name] = request
+        return requests
+
+    def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
+        for child in self.sub_parts().values():
+            if type(child).plan_step is not Part.plan_step:
+                child.plan_step(ctx, binding)
+
+    def forward(self, hidden: torch.Tensor, pending: "torch.Tensor | Normed | None", ctx: StepContext,
+                binding: CacheBinding | None, next_norm: Part | None = None) -> torch.Tensor:
+        if isinstance(pending, Normed):
+            raise ValueError("this block normalises the stream itself")
+        h = self.mixer_norm.add_norm(hidden, pending, ctx.dtype)
+        if self.input_conv is not None:
+            h = self.input_conv.forward(h, ctx, binding)
+        update = self.mixer.forward(h, ctx, binding)
+        bias = None
+        if self.feed_forward is not None:
+            h = self.ff_norm.add_norm(hidden, update, ctx.dtype)
+            if self.side is not None and hasattr(self.feed_forward, "last_bias"):
+                # the side input adds the update to the stream anyway: the last bias rides along
+                update, bias = self.feed_forward.forward(h, ctx, add_bias=False), self.feed_forward.last_bias
+            else:
+                update = self.feed_forward.forward(h, ctx)
+        if self.side is not None:
+            update = self.side.forward(hidden, update, ctx, bias)
+        return update

@@ -9,7 +9,7 @@ from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.parts.base import ParamSpec, Part, StepContext
 
-__all__ = ["SwiGLU"]
+__all__ = ["BiasedDense", "RoutedExperts", "SwiGLU"]
 
 
 @register_part("feed_forward", "swiglu")
@@ -69,3 +69,98 @@ class SwiGLU(Part):
         if finish is not None:
             return finish(gated, self.down_proj)
         return gemm.linear(gated, self.down_proj, chain=True)
+
+
+@register_part("feed_forward", "biased_dense")
+class BiasedDense(Part):
+    """``W_down act(W_up x + b_up) + b_down`` with the exact (erf) GELU by default; weights
+    ``[out, in]``. The bias of the last product is not added here: ``forward`` returns the
+    product and ``last_bias`` names the vector, so that whoever adds the update to the stream adds
+    the bias in the same pass (``forward(..., add_bias=True)`` adds it at once)."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, activation: str = "gelu_erf") -> None:
+        self.width, self.inner, self.activation = int(width), int(inner), activation
+        self.up: torch.Tensor | None = None
+        self.down: torch.Tensor | None = None
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        return {"up": ParamSpec((self.inner, self.width)), "up_b": ParamSpec((self.inner,), "vector"),
+                "down": ParamSpec((self.width, self.inner)), "down_b": ParamSpec((self.width,), "vector")}
+
+    @property
+    def last_bias(self) -> torch.Tensor:
+        return self.down_b
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, add_bias: bool = True) -> torch.Tensor:
+        from paged_kv_serving_b200.ops import mixer_ops
+
+        inner = mixer_ops.bias_act(gemm.linear(x, self.up), self.up_b, self.activation)
+        out = gemm.linear(inner, self.down)
+        return mixer_ops.bias_act(out, self.down_b, "none") if add_bias else out
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(Part):
+    """A mixture of small feed-forward experts ``W_down act(W_up x)`` without biases (``act`` the
+    square of relu by default). Router logits ``W_router x`` and their softmax over all experts
+    are float32; a token uses its ``top`` best experts, weighted by their softmax scores as they
+    are (not renormalised). An optional shared expert of the same form runs for every token and
+    is added times ``sigmoid(W_sg x)``, one number per token.
+
+    Kernels: one product over the stacked up-projections of all experts (and the shared one), the
+    activation scaled by the router's weight of each column's expert (zero for an expert the
+    token does not use), one product over the stacked down-projections. Every expert's weights
+    are read once per step whatever the routing, and nothing of the step depends on values read
+    back to the host, so decode steps can be captured.
+    """
+
+    graph_safe = True
+
+    def __init__(self, width: int, experts: int, top: int, inner: int, shared_inner: int = 0,
+                 activation: str = "relu_squared") -> None:
+        if not 1 <= top <= experts:
+            raise ValueError("top must be between 1 and the number of experts")
+        self.width, self.experts, self.top, self.inner = int(width), int(experts), int(top), int(inner)
+        self.shared_inner, self.activation = int(shared_inner), activation
+        self.columns = self.experts * self.inner + self.shared_inner
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        specs = {"router": ParamSpec((self.experts, self.width))}
+        for e in range(self.experts):
+            specs[f"e{e}_up"] = ParamSpec((self.inner, self.width))
+            specs[f"e{e}_down"] = ParamSpec((self.width, self.inner))
+        if self.shared_inner:
+            specs["shared_up"] = ParamSpec((self.shared_inner, self.width))
+            specs["shared_down"] = ParamSpec((self.width, self.shared_inner))
+            specs["shared_sg"] = ParamSpec((1, self.width))
+        return specs
+
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        ups = [params[f"e{e}_up"] for e in range(self.experts)]
+        downs = [params[f"e{e}_down"] for e in range(self.experts)]
+        route = [params["router"]]
+        if self.shared_inner:
+            ups.append(params["shared_up"])
+            downs.append(params["shared_down"])
+            route.append(params["shared_sg"])
+        padded = -(-self.columns // 8) * 8             # rows of a product's result start on 16-byte boundaries
+        up = torch.zeros((padded, self.width), dtype=ups[0].dtype, device=ups[0].device)
+        up[:self.columns] = torch.cat(ups, dim=0)
+        self.up = up                                                       # [columns (padded), width]
+        self.down = torch.cat(downs, dim=1).contiguous()                   # [width, columns]
+        rows = -(-(self.experts + 1) // 8) * 8
+        router = torch.zeros((rows, self.width), dtype=ups[0].dtype, device=ups[0].device)
+        router[:self.experts + len(route) - 1] = torch.cat(route, dim=0)
+        self.router = router                                               # router rows, then the shared gate's row
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        from paged_kv_serving_b200.ops import mixer_ops
+
+        logits = gemm.linear(x, self.router, out_dtype=torch.float32)      # [tokens, experts + 1 (padded)]
+        weights = mixer_ops.route_top(logits, self.experts, self.top)
+        up = gemm.linear(x, self.up)
+        gate = logits[:, self.experts] if self.shared_inner else None
+        inner = mixer_ops.expert_act(up, weights, gate, self.experts, self.inner, self.shared_inner, self.activation)
+        return gemm.linear(inner, self.down)

@@ -1,0 +1,127 @@
+"""Attention whose keys and values are read out of one cached latent vector per position."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from paged_kv_serving_b200 import ops
+from paged_kv_serving_b200.config.registry import register_part
+from paged_kv_serving_b200.ops import gemm, mixer_ops
+from paged_kv_serving_b200.parts.base import CacheBinding, PagedKVRequest, ParamSpec, Part, StepContext
+
+__all__ = ["LatentAttention"]
+
+
+def _round_up(value: int, multiple: int) -> int:
+    return -(-value // multiple) * multiple
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Part):
+    """Causal softmax attention with low-rank queries, keys and values and an output gate.
+
+    With ``h`` the input: ``c_q = rmsnorm(W_dq h) * dq_norm`` and ``q = W_uq c_q``, laid out head
+    by head as ``[dim unrotated | rot_dim rotated]``. ``W_dkv h`` gives ``kv_rank`` numbers whose
+    RMS norm (times ``dkv_norm``) is the latent ``c``, and ``rot_dim`` more that form one rotated
+    key part shared by all heads. Head ``a`` has keys ``W_uk[a] c`` and values ``W_uv[a] c``; the
+    score is ``(q_unrotated . k_unrotated + q_rotated . k_rotated) * scale``; the head's result is
+    multiplied by ``sigmoid(W_g h)[a]`` and the heads go through ``W_o``. Rotation acts on the
+    first ``rot_dims`` coordinates of the rotated parts (coordinate ``i`` pairs with
+    ``i + rot_dims / 2``) with angle ``position * base^(-2i / rot_dims)``.
+
+    Only ``[c | rotated key part]`` is cached, ``kv_rank + rot_dim`` numbers a position for all
+    heads (a page group without values). The kernels use the absorbed form: the unrotated query of
+    a head is multiplied by ``W_uk[a]`` first (``q_lat = W_uk[a]^T q_unrotated``, one batched
+    product), so that the score is a dot product with the cached row, the softmax-weighted sum
+    runs over the latents themselves, and ``W_uv[a]`` is applied to that sum (a second batched
+    product). Norms, angles, scores and softmax are float32 in both compute types.
+    """
+
+    graph_safe = True
+
+    def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int, scale: float,
+                 rot_base: float, rot_dims: int, eps: float, window: int | None = None) -> None:
+        if rot_dims % 2 or rot_dims > rot_dim:
+            raise ValueError("the rotated coordinates must be an even number within the rotated part")
+        if kv_rank > 512:
+            raise ValueError("the latent attention kernel takes a latent of up to 512 numbers")
+        self.width, self.heads, self.dim, self.rot_dim, self.vdim = int(width), int(heads), int(dim), int(rot_dim), int(vdim)
+        self.q_rank, self.kv_rank, self.scale, self.eps = int(q_rank), int(kv_rank), float(scale), float(eps)
+        self.rot_base, self.rot_dims, self.window = float(rot_base), int(rot_dims), window
+        # columns of the fused down-projection: [query latent | key/value latent, key part | gate], padded
+        self.q_off, self.kv_off = 0, self.q_rank
+        self.g_off = self.q_rank + self.kv_rank + self.rot_dim
+        self.fused_rows = _round_up(self.g_off + self.heads, 8)
+        half = self.rot_dims // 2
+        self._freq_host = np.asarray([self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(half)] or [0.0],
+                                     dtype=np.float64).astype(np.float32)
+        self.freq: torch.Tensor | None = None
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        head = self.dim + self.rot_dim
+        return {
+            "dq": ParamSpec((self.q_rank, self.width)), "dq_norm": ParamSpec((self.q_rank,), "vector"),
+            "uq": ParamSpec((self.heads * head, self.q_rank)),
+            "dkv": ParamSpec((self.kv_rank + self.rot_dim, self.width)), "dkv_norm": ParamSpec((self.kv_rank,), "vector"),
+            "uk": ParamSpec((self.heads * self.dim, self.kv_rank)), "uv": ParamSpec((self.heads * self.vdim, self.kv_rank)),
+            "g": ParamSpec((self.heads, self.width)), "o": ParamSpec((self.width, self.heads * self.vdim)),
+        }
+
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        dq = params["dq"]
+        fused = torch.zeros((self.fused_rows, self.width), dtype=dq.dtype, device=dq.device)
+        fused[:self.q_rank] = dq
+        fused[self.kv_off:self.g_off] = params["dkv"]
+        fused[self.g_off:self.g_off + self.heads] = params["g"]
+        self.down = fused                                                     # [fused_rows, width]
+        self.uq = params["uq"].contiguous()
+        self.uk = params["uk"].view(self.heads, self.dim, self.kv_rank).contiguous()        # q_lat = q_unrot @ uk[a]
+        self.uv_t = params["uv"].view(self.heads, self.vdim, self.kv_rank).transpose(1, 2).contiguous()   # [a, rank, vdim]
+        self.o = params["o"].contiguous()
+        self.dq_norm, self.dkv_norm = params["dq_norm"], params["dkv_norm"]
+        self.freq = torch.from_numpy(self._freq_host).to(dq.device)
+
+    def cache_request(self) -> PagedKVRequest:
+        return PagedKVRequest(1, self.kv_rank + self.rot_dim, self.window, values=False)
+
+    def _work_names(self) -> tuple[str, str]:
+        return (f"latent_attention/work_seq/h{self.heads}", f"latent_attention/work_row0/h{self.heads}")
+
+    def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
+        seq_name, row_name = self._work_names()
+        if seq_name in ctx.arena:
+            return
+        per_block = mixer_ops.latent_rows_per_block()
+        rows = np.asarray(ctx.seq_lens, dtype=np.int64) * self.heads
+        blocks = (rows + per_block - 1) // per_block
+        work_seq = np.repeat(np.arange(len(rows), dtype=np.int64), blocks)
+        starts = np.cumsum(blocks) - blocks
+        work_row0 = (np.arange(int(blocks.sum()), dtype=np.int64) - np.repeat(starts, blocks)) * per_block
+        ctx.arena.add(seq_name, work_seq)
+        ctx.arena.add(row_name, work_row0)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding) -> torch.Tensor:
+        group = ctx.groups[binding.group]
+        pool = group.k_pool[binding.index]
+        tokens = x.shape[0]
+        head = self.dim + self.rot_dim
+        # every down-projection of the input in one product, kept in float32 for the norms
+        fused = gemm.linear(x, self.down, out_dtype=torch.float32)
+        slots = ctx.ints(group.slots_name) if binding.write else None
+        c_q = mixer_ops.latent_prepare(fused, self.q_off, self.q_rank, self.kv_off, self.kv_rank, self.rot_dim, self.rot_dims,
+                                       self.dq_norm, self.dkv_norm, self.freq, self.eps, ctx.ints(ctx.POSITIONS), slots, pool,
+                                       ctx.status)
+        q = gemm.linear(c_q, self.uq)                                          # [tokens, heads * (dim + rot_dim)]
+        q_unrotated = q.view(tokens, self.heads, head)[:, :, :self.dim].transpose(0, 1)     # [heads, tokens, dim], a view
+        q_lat = torch.bmm(q_unrotated, self.uk, out_dtype=torch.float32) if q.dtype != torch.float32 \
+            else torch.bmm(q_unrotated, self.uk)
+        seq_name, row_name = self._work_names()
+        gate = fused[:, self.g_off:self.g_off + self.heads]
+        attended = mixer_ops.latent_attention(
+            q_lat, q, self.dim, head, pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
+            ctx.ints(seq_name), ctx.ints(row_name), self.freq, gate, self.heads, self.kv_rank, self.rot_dim, self.rot_dims,
+            group.page_size, self.window or 0, self.scale, ctx.status)
+        values = torch.bmm(attended, self.uv_t)                                # [heads, tokens, vdim]
+        merged = values.transpose(0, 1).reshape(tokens, self.heads * self.vdim)
+        return gemm.linear(merged, self.o)

@@ -9,7 +9,7 @@ from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.parts.base import ParamSpec, Part
 
-__all__ = ["RMSNorm"]
+__all__ = ["RMSNorm", "ScalarRMSNorm"]
 
 
 @register_part("norm", "rmsnorm")
@@ -41,3 +41,16 @@ class RMSNorm(Part):
         product's kernel carries the residual add, and the norm is left to the product that reads
         the result, where the kernels can do that. ``chain`` as in ``ops.gemm.linear``."""
         return gemm.linear_add_norm(x, w_nk, hidden, self.weight, self.eps, out_dtype, chain=chain)
+
+
+@register_part("norm", "scalar_rmsnorm")
+class ScalarRMSNorm(RMSNorm):
+    """RMS norm whose weight is a single number for all coordinates:
+    ``y = x / sqrt(mean(x^2) + eps) * g``. The stored tensor has no axes; at load it is spread
+    over the width, so that the kernels of ``RMSNorm`` (and its fusions) serve it unchanged."""
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        return {"weight": ParamSpec((), "vector")}
+
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        self.weight = params["weight"].reshape(1).expand(self.width).contiguous()
