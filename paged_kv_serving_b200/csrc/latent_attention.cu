@@ -198,6 +198,267 @@ latent_attention_kernel(const Q* __restrict__ q_lat, const A* __restrict__ q_rot
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// The tensor-core form for bfloat16: one block of 4 warps per 64 consecutive rows of an entry
+// (each warp 16 rows), keys in tiles of 32 absolute positions aligned to multiples of 32 from
+// position 0, double-buffered with cp.async from the pages the block table names. S = Q K^T and
+// O += P V run on mma.sync m16n8k16 with float32 accumulators; the values of a tile are the
+// first `rank` columns of its keys, read from the same shared-memory tile (transposed loads).
+// A block accumulates VT of the `rank` value columns (grid.y blocks share the rows when
+// rank > VT and each computes the scores again). Scores, maxima, sums and exponentials are
+// float32; queries and probabilities enter the products as bfloat16.
+// ---------------------------------------------------------------------------------------------
+constexpr int LM_BM = 64;
+constexpr int LM_BN = 32;
+constexpr int LM_THREADS = 128;
+constexpr int LM_PAD = 8;
+
+__device__ __forceinline__ uint32_t lm_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void lm_cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(lm_smem_u32(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void lm_cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void lm_cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void lm_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(lm_smem_u32(p)));
+}
+__device__ __forceinline__ void lm_ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(lm_smem_u32(p)));
+}
+__device__ __forceinline__ void lm_mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lm_pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct LatentParams {
+  const void* q_lat;            // [heads, tokens, rank], float32 or bfloat16
+  const bf16* q_rot;            // rotated part of head h of token t at q_rot + t * q_rot_ld + h * q_rot_head_stride
+  int q_rot_ld, q_rot_head_stride;
+  bf16* out;                    // [heads, tokens, rank]
+  const bf16* pool;             // [pages, page_size, rank + rot]
+  const int32_t* block_table;
+  int table_stride;
+  const int32_t* seq_starts;
+  const int32_t* first_pos;
+  const int32_t* work_seq;
+  const int32_t* work_row0;
+  const float* freq;
+  const float* gate;
+  int gate_ld, tokens, heads, rank, rot, rot_dims, page_size, window;
+  float scale_log2;
+  int num_pages;
+  int* status;
+};
+
+__device__ __forceinline__ void lm_load_tile(bf16* tile, const LatentParams& p, const int32_t* table, int base, int key_lo,
+                                             int key_hi, int dk, int ld) {
+  const int chunks = dk >> 3;
+  for (int idx = threadIdx.x; idx < LM_BN * chunks; idx += LM_THREADS) {
+    const int row = idx / chunks, chunk = idx - row * chunks;
+    const int pos = base + row;
+    bf16* dst = tile + row * ld + chunk * 8;
+    int page = -1;
+    if (pos >= key_lo && pos < key_hi) page = checked_page(table[pos / p.page_size], p.num_pages, p.status);
+    if (page >= 0)
+      lm_cp_async16(dst, p.pool + ((size_t)page * p.page_size + (pos % p.page_size)) * dk + chunk * 8);
+    else
+      *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+template <int VT, typename Q>
+__global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(const LatentParams p) {
+  constexpr int DTILES = VT / 8;
+  extern __shared__ __align__(16) unsigned char lm_smem[];
+  const int dk = p.rank + p.rot;
+  const int ld = dk + LM_PAD;
+  bf16* q_s = reinterpret_cast<bf16*>(lm_smem);     // [LM_BM][ld]
+  bf16* k_s = q_s + LM_BM * ld;                      // [2][LM_BN][ld]
+
+  const int s = p.work_seq[blockIdx.x], row0 = p.work_row0[blockIdx.x];
+  const int v0 = blockIdx.y * VT;                    // first value column of this block
+  const int tok0 = p.seq_starts[s];
+  const int n_q = p.seq_starts[s + 1] - tok0;
+  const int pos0 = p.first_pos[s];
+  const int heads = p.heads;
+  const int rows_total = n_q * heads;
+  const int rows_valid = min(LM_BM, rows_total - row0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+
+  const int q_first = pos0 + row0 / heads;
+  const int q_last = pos0 + (row0 + rows_valid - 1) / heads;
+  const int key_hi = q_last + 1;                                              // exclusive
+  const int key_lo = p.window > 0 ? max(0, q_first - p.window + 1) : 0;
+  const int tile_begin = key_lo / LM_BN, tile_end = (key_hi - 1) / LM_BN;     // inclusive
+  const int32_t* table = p.block_table + (size_t)s * p.table_stride;
+
+  lm_load_tile(k_s, p, table, tile_begin * LM_BN, key_lo, key_hi, dk, ld);
+  lm_cp_async_commit();
+
+  // the queries of this block: absorbed part as it is, rotated part rotated by the row's position
+  {
+    const Q* q_lat = reinterpret_cast<const Q*>(p.q_lat);
+    const int half = p.rot_dims >> 1;
+    for (int idx = threadIdx.x; idx < LM_BM * dk; idx += LM_THREADS) {
+      const int row = idx / dk, d = idx - row * dk;
+      float v = 0.0f;
+      if (row < rows_valid) {
+        const int r = row0 + row;
+        const int token = tok0 + r / heads, head = r % heads;
+        if (d < p.rank) {
+          v = to_float(q_lat[((size_t)head * p.tokens + token) * p.rank + d]);
+        } else {
+          const int i = d - p.rank;
+          const bf16* qr = p.q_rot + (size_t)token * p.q_rot_ld + (size_t)head * p.q_rot_head_stride;
+          v = to_float(qr[i]);
+          if (i < p.rot_dims) {
+            const float position = (float)(pos0 + r / heads);
+            float sn, cs;
+            if (i < half) {
+              sincosf(position * p.freq[i], &sn, &cs);
+              v = v * cs - to_float(qr[i + half]) * sn;
+            } else {
+              sincosf(position * p.freq[i - half], &sn, &cs);
+              v = v * cs + to_float(qr[i - half]) * sn;
+            }
+          }
+        }
+      }
+      q_s[row * ld + d] = __float2bfloat16_rn(v);
+    }
+  }
+
+  const int row_a = warp * 16 + g, row_b = row_a + 8;
+  const int qpos_a = pos0 + (row0 + row_a) / heads, qpos_b = pos0 + (row0 + row_b) / heads;
+  const int warp_qpos_min = pos0 + (row0 + warp * 16) / heads;
+  const int warp_qpos_max = pos0 + min(row0 + warp * 16 + 15, rows_total - 1) / heads;
+  const bool warp_active = warp * 16 < rows_valid;
+  const int ksteps = dk >> 4;
+
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
+  float o[DTILES][4];
+#pragma unroll
+  for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+
+  for (int tile = tile_begin; tile <= tile_end; ++tile) {
+    const int stage = (tile - tile_begin) & 1;
+    const int base = tile * LM_BN;
+    if (tile < tile_end) {
+      lm_load_tile(k_s + (stage ^ 1) * LM_BN * ld, p, table, base + LM_BN, key_lo, key_hi, dk, ld);
+      lm_cp_async_commit();
+      lm_cp_async_wait<1>();
+    } else {
+      lm_cp_async_wait<0>();
+    }
+    __syncthreads();            // the tile (and, the first time, the queries) are in shared memory
+    const bf16* kt = k_s + stage * LM_BN * ld;
+
+    const bool skip = !warp_active || base > warp_qpos_max ||
+                      (p.window > 0 && base + LM_BN - 1 < warp_qpos_min - p.window + 1);
+    if (!skip) {
+      float sc[LM_BN / 8][4];
+#pragma unroll
+      for (int j = 0; j < LM_BN / 8; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
+      for (int kk = 0; kk < ksteps; ++kk) {
+        uint32_t a[4];
+        lm_ldmatrix_x4(a, q_s + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ld + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+        for (int jj = 0; jj < LM_BN / 16; ++jj) {
+          uint32_t b[4];
+          lm_ldmatrix_x4(b, kt + (jj * 16 + (lane & 7) + 8 * (lane >> 4)) * ld + kk * 16 + 8 * ((lane >> 3) & 1));
+          lm_mma_bf16(sc[2 * jj], a, b[0], b[1]);
+          lm_mma_bf16(sc[2 * jj + 1], a, b[2], b[3]);
+        }
+      }
+      const bool need_mask = base + LM_BN - 1 > warp_qpos_min || (p.window > 0 && base < warp_qpos_max - p.window + 1);
+      float tmax_a = -INFINITY, tmax_b = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < LM_BN / 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = sc[j][e] * p.scale_log2;
+          if (need_mask) {
+            const int kpos = base + j * 8 + 2 * t4 + (e & 1);
+            const int qpos = (e < 2) ? qpos_a : qpos_b;
+            const bool ok = kpos <= qpos && (p.window == 0 || kpos > qpos - p.window);
+            v = ok ? v : -INFINITY;
+          }
+          sc[j][e] = v;
+          if (e < 2) tmax_a = fmaxf(tmax_a, v); else tmax_b = fmaxf(tmax_b, v);
+        }
+      }
+      tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 1));
+      tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 2));
+      tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 1));
+      tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 2));
+      const float new_a = fmaxf(m_a, tmax_a), new_b = fmaxf(m_b, tmax_b);
+      const float shift_a = new_a == -INFINITY ? 0.0f : new_a, shift_b = new_b == -INFINITY ? 0.0f : new_b;
+      const float resc_a = exp2f(m_a - shift_a), resc_b = exp2f(m_b - shift_b);
+      m_a = new_a; m_b = new_b;
+      float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+      for (int j = 0; j < LM_BN / 8; ++j) {
+        sc[j][0] = exp2f(sc[j][0] - shift_a); sc[j][1] = exp2f(sc[j][1] - shift_a);
+        sc[j][2] = exp2f(sc[j][2] - shift_b); sc[j][3] = exp2f(sc[j][3] - shift_b);
+        sum_a += sc[j][0] + sc[j][1];
+        sum_b += sc[j][2] + sc[j][3];
+      }
+      l_a = l_a * resc_a + sum_a;
+      l_b = l_b * resc_b + sum_b;
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i) { o[i][0] *= resc_a; o[i][1] *= resc_a; o[i][2] *= resc_b; o[i][3] *= resc_b; }
+#pragma unroll
+      for (int kk = 0; kk < LM_BN / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = lm_pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+        a[1] = lm_pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+        a[2] = lm_pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+        a[3] = lm_pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+        for (int dd = 0; dd < DTILES / 2; ++dd) {
+          if (v0 + dd * 16 < p.rank) {             // (rank is a multiple of 16: whole groups of columns)
+            uint32_t b[4];
+            lm_ldmatrix_x4_trans(b, kt + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ld + v0 + dd * 16 + 8 * (lane >> 4));
+            lm_mma_bf16(o[2 * dd], a, b[0], b[1]);
+            lm_mma_bf16(o[2 * dd + 1], a, b[2], b[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  float f_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, f_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
+#pragma unroll
+  for (int half_rows = 0; half_rows < 2; ++half_rows) {
+    const int row = half_rows ? row_b : row_a;
+    if (row >= rows_valid) continue;
+    const int r = row0 + row;
+    const int token = tok0 + r / heads, head = r % heads;
+    float f = half_rows ? f_b : f_a;
+    if (p.gate) f *= 1.0f / (1.0f + expf(-p.gate[(size_t)token * p.gate_ld + head]));
+    bf16* dst = p.out + ((size_t)head * p.tokens + token) * p.rank + v0;
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) {
+      if (v0 + i * 8 < p.rank) {
+        const float x = half_rows ? o[i][2] : o[i][0], y = half_rows ? o[i][3] : o[i][1];
+        *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = lm_pack_bf16(x * f, y * f);
+      }
+    }
+  }
+}
+
 }  // namespace pkv
 
 using namespace pkv;
@@ -267,4 +528,59 @@ PKV_EXPORT int pkv_latent_attention(const void* q_lat, int q_lat_dtype, const vo
   if (act_dtype == PKV_BF16 && cache_dtype == PKV_BF16 && q_lat_dtype == PKV_BF16) PKV_LAT(bf16, bf16, bf16);
 #undef PKV_LAT
   return PKV_ERR_DTYPE;
+}
+
+PKV_EXPORT int pkv_latent_mma_rows_per_block() { return LM_BM; }
+
+// Whether the tensor-core kernel takes these sizes (else the general kernel above serves them).
+PKV_EXPORT int pkv_latent_mma_supports(int rank, int rot) {
+  const int dk = rank + rot;
+  if (rank < 16 || (rank & 15) || (dk & 15)) return 0;
+  const size_t smem = (size_t)(LM_BM + 2 * LM_BN) * (dk + LM_PAD) * sizeof(bf16);
+  return smem <= 200 * 1024 ? 1 : 0;
+}
+
+template <int VT, typename Q>
+static int launch_latent_mma(const LatentParams& p, int n_work, cudaStream_t s) {
+  const int dk = p.rank + p.rot;
+  const size_t smem = (size_t)(LM_BM + 2 * LM_BN) * (dk + LM_PAD) * sizeof(bf16);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<VT, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid(n_work, (p.rank + VT - 1) / VT);
+  latent_attention_mma_kernel<VT, Q><<<grid, LM_THREADS, smem, s>>>(p);
+  return launch_status();
+}
+
+PKV_EXPORT int pkv_latent_attention_mma(const void* q_lat, int q_lat_dtype, const void* q_rot, int q_rot_ld,
+                                        int q_rot_head_stride, void* out, const void* pool, const int32_t* block_table,
+                                        int table_stride, const int32_t* seq_starts, const int32_t* first_pos,
+                                        const int32_t* work_seq, const int32_t* work_row0, int n_work, const float* freq,
+                                        const float* gate, int gate_ld, int tokens, int heads, int rank, int rot,
+                                        int rot_dims, int page_size, int window, float scale, int num_pages, int* status,
+                                        void* stream) {
+  if (n_work <= 0) return 0;
+  if (heads < 1 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1) || page_size < 1 || window < 0 || num_pages < 1)
+    return PKV_ERR_SIZE;
+  if (!pkv_latent_mma_supports(rank, rot)) return PKV_ERR_SIZE;
+  LatentParams p;
+  p.q_lat = q_lat; p.q_rot = (const bf16*)q_rot; p.q_rot_ld = q_rot_ld; p.q_rot_head_stride = q_rot_head_stride;
+  p.out = (bf16*)out; p.pool = (const bf16*)pool; p.block_table = block_table; p.table_stride = table_stride;
+  p.seq_starts = seq_starts; p.first_pos = first_pos; p.work_seq = work_seq; p.work_row0 = work_row0; p.freq = freq;
+  p.gate = gate; p.gate_ld = gate_ld; p.tokens = tokens; p.heads = heads; p.rank = rank; p.rot = rot; p.rot_dims = rot_dims;
+  p.page_size = page_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.num_pages = num_pages;
+  p.status = status;
+  cudaStream_t s = (cudaStream_t)stream;
+#define PKV_LM(VT)                                                             \
+  do {                                                                         \
+    if (q_lat_dtype == PKV_F32) return launch_latent_mma<VT, float>(p, n_work, s); \
+    if (q_lat_dtype == PKV_BF16) return launch_latent_mma<VT, bf16>(p, n_work, s); \
+    return PKV_ERR_DTYPE;                                                      \
+  } while (0)
+  if (rank <= 64) PKV_LM(64);
+  if (rank <= 128) PKV_LM(128);
+  PKV_LM(256);
+#undef PKV_LM
 }

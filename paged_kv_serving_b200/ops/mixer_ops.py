@@ -16,7 +16,8 @@ from paged_kv_serving_b200.ops import _check, _fn, _need, _ptr, _stream, dtype_c
 from paged_kv_serving_b200.ops.arena import empty as _empty
 
 __all__ = ["ACTIVATIONS", "act_times_table", "bias_act", "conv_residual", "expert_act", "latent_attention",
-           "latent_prepare", "latent_rows_per_block", "mlstm", "residual_add", "route_top"]
+           "latent_attention_mma", "latent_mma_rows_per_block", "latent_mma_supports", "latent_prepare",
+           "latent_rows_per_block", "mlstm", "residual_add", "route_top"]
 
 #: activation names of ``bias_act`` / ``act_times_table`` / ``expert_act``
 ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "relu_squared": 3, "sigmoid": 4}
@@ -225,4 +226,52 @@ def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_rot_offset: int, q_
               _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), _ptr(work_row0), work_seq.numel() if n_work is None else int(n_work), _ptr(freq), _ptr(gate),
               gate_ld, tokens, heads, rank, rot, rot_dims, page_size, int(window), float(scale), num_pages, _ptr(status),
               _stream()), "latent_attention")
+    return out
+
+
+def latent_mma_rows_per_block() -> int:
+    fn = ops.library("latent_attention").pkv_latent_mma_rows_per_block
+    fn.restype = c_int
+    return int(fn())
+
+
+def latent_mma_supports(rank: int, rot: int) -> bool:
+    """Whether the tensor-core kernel takes a latent of ``rank`` numbers with ``rot`` rotated ones
+    behind them (multiples of 16 that fit its shared memory)."""
+    fn = ops.library("latent_attention").pkv_latent_mma_supports
+    fn.restype = c_int
+    fn.argtypes = [c_int, c_int]
+    return bool(fn(int(rank), int(rot)))
+
+
+def latent_attention_mma(q_lat: torch.Tensor, q: torch.Tensor, q_rot_offset: int, q_head_stride: int, pool: torch.Tensor,
+                         block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor, work_seq: torch.Tensor,
+                         work_row0: torch.Tensor, freq: torch.Tensor, gate: torch.Tensor | None, heads: int, rank: int,
+                         rot: int, rot_dims: int, page_size: int, window: int, scale: float, status: torch.Tensor,
+                         n_work: int | None = None) -> torch.Tensor:
+    """``latent_attention`` on the tensor cores, for bfloat16 queries and cache (``q_lat`` float32
+    or bfloat16); the work list is in blocks of ``latent_mma_rows_per_block()`` rows."""
+    _need(q_lat, None, "q_lat"); _need(q, torch.bfloat16, "q"); _need(pool, torch.bfloat16, "pool")
+    tokens = q.shape[0]
+    if q_lat.shape != (heads, tokens, rank):
+        raise ValueError("q_lat must be [heads, tokens, rank]")
+    if (q.stride(0) * 2) % 4 or (q_head_stride * 2) % 2:
+        raise ValueError("the query rows are not aligned")
+    gate_ld = 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.stride(1) != 1:
+            raise ValueError("gate must be a float32 [tokens, heads] view with unit inner stride")
+        gate_ld = gate.stride(0)
+    out = _empty((heads, tokens, rank), torch.bfloat16, q.device)
+    num_pages = pool.numel() // (page_size * (rank + rot))
+    fn = _fn("latent_attention", "pkv_latent_attention_mma",
+             [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+              c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+              c_void_p, c_void_p])
+    q_rot = q.view(-1)[q_rot_offset:]
+    _check(fn(_ptr(q_lat), dtype_code(q_lat.dtype), c_void_p(q_rot.data_ptr()), q.stride(0), q_head_stride, _ptr(out),
+              _ptr(pool), _ptr(block_table), block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq),
+              _ptr(work_row0), work_seq.numel() if n_work is None else int(n_work), _ptr(freq), _ptr(gate), gate_ld, tokens,
+              heads, rank, rot, rot_dims, page_size, int(window), float(scale), num_pages, _ptr(status), _stream()),
+           "latent_attention_mma")
     return out

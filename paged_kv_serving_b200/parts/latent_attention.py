@@ -39,6 +39,8 @@ class LatentAttention(Part):
     """
 
     graph_safe = True
+    #: Set to False to keep bfloat16 steps on the general (float32-arithmetic) kernel; tests compare the two.
+    USE_TENSOR_CORES = True
 
     def __init__(self, width: int, heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int, scale: float,
                  rot_base: float, rot_dims: int, eps: float, window: int | None = None) -> None:
@@ -57,6 +59,7 @@ class LatentAttention(Part):
         self._freq_host = np.asarray([self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(half)] or [0.0],
                                      dtype=np.float64).astype(np.float32)
         self.freq: torch.Tensor | None = None
+        self._mma_ok: bool | None = None
 
     def param_specs(self) -> dict[str, ParamSpec]:
         head = self.dim + self.rot_dim
@@ -85,14 +88,22 @@ class LatentAttention(Part):
     def cache_request(self) -> PagedKVRequest:
         return PagedKVRequest(1, self.kv_rank + self.rot_dim, self.window, values=False)
 
-    def _work_names(self) -> tuple[str, str]:
-        return (f"latent_attention/work_seq/h{self.heads}", f"latent_attention/work_row0/h{self.heads}")
+    def _tensor_cores(self, ctx: StepContext) -> bool:
+        if ctx.dtype != torch.bfloat16 or not self.USE_TENSOR_CORES:
+            return False
+        if self._mma_ok is None:
+            self._mma_ok = mixer_ops.latent_mma_supports(self.kv_rank, self.rot_dim)
+        return self._mma_ok
+
+    def _work_names(self, ctx: StepContext) -> tuple[str, str]:
+        kind = "mma" if self._tensor_cores(ctx) else "general"
+        return (f"latent_attention/{kind}/work_seq/h{self.heads}", f"latent_attention/{kind}/work_row0/h{self.heads}")
 
     def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
-        seq_name, row_name = self._work_names()
+        seq_name, row_name = self._work_names(ctx)
         if seq_name in ctx.arena:
             return
-        per_block = mixer_ops.latent_rows_per_block()
+        per_block = mixer_ops.latent_mma_rows_per_block() if self._tensor_cores(ctx) else mixer_ops.latent_rows_per_block()
         rows = np.asarray(ctx.seq_lens, dtype=np.int64) * self.heads
         blocks = (rows + per_block - 1) // per_block
         work_seq = np.repeat(np.arange(len(rows), dtype=np.int64), blocks)
@@ -116,9 +127,10 @@ class LatentAttention(Part):
         q_unrotated = q.view(tokens, self.heads, head)[:, :, :self.dim].transpose(0, 1)     # [heads, tokens, dim], a view
         q_lat = torch.bmm(q_unrotated, self.uk, out_dtype=torch.float32) if q.dtype != torch.float32 \
             else torch.bmm(q_unrotated, self.uk)
-        seq_name, row_name = self._work_names()
+        seq_name, row_name = self._work_names(ctx)
         gate = fused[:, self.g_off:self.g_off + self.heads]
-        attended = mixer_ops.latent_attention(
+        kernel = mixer_ops.latent_attention_mma if self._tensor_cores(ctx) else mixer_ops.latent_attention
+        attended = kernel(
             q_lat, q, self.dim, head, pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
             ctx.ints(seq_name), ctx.ints(row_name), self.freq, gate, self.heads, self.kv_rank, self.rot_dim, self.rot_dims,
             group.page_size, self.window or 0, self.scale, ctx.status)
