@@ -489,6 +489,31 @@ def run_reference_workload() -> dict:
             "output_tokens": tokens, "seconds": best, "output_tokens_per_s": tokens / best}
 
 
+def run_design(args) -> dict:
+    """``--design revupel``: the design and the Llama-style decoder side by side, per size."""
+    import torch
+
+    from paged_kv_serving_b200 import design_bench
+
+    peaks = load_peaks()
+    torch.cuda.set_device(0)
+    clocks = ClockSampler()
+    clocks.start()
+    sizes = {}
+    for size in [s for s in args.design_sizes.split(",") if s]:
+        sizes[size] = {
+            "revupel": design_bench.measure(design_bench.revupel_config(size), peaks, prefill_tokens=args.prefill_tokens,
+                                            batch=args.batch, context=args.prompt_len, steps=min(args.steps, 32), warmup=args.warmup),
+            "llama_style": design_bench.measure(design_bench.llama_like(size), peaks, prefill_tokens=args.prefill_tokens,
+                                                batch=args.batch, context=args.prompt_len, steps=min(args.steps, 32),
+                                                warmup=args.warmup),
+        }
+        torch.cuda.empty_cache()
+    clocks.stop()
+    return {"impl": "ours", "design": args.design, "dtype": "bf16", "data": "synthetic: random ids, random N(0, 0.02) weights",
+            "peaks": peaks, "sizes": sizes, "clocks": clocks.summary()}
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -507,6 +532,10 @@ def main() -> int:
     parser.add_argument("--only-workloads", action="store_true", help="leave out the headline run (for profiling a workload)")
     parser.add_argument("--workload-layers", type=int, default=0, help="fewer layers for those workloads (0: all)")
     parser.add_argument("--serve-requests", type=int, default=256)
+    parser.add_argument("--design", choices=("revupel",), default=None,
+                        help="instead of the default run: prefill and decode throughput of this design at layer sizes of "
+                             "real models, beside the Llama-style decoder at equal sizes, with every kernel against its roofline")
+    parser.add_argument("--design-sizes", default="1b,7b", help="which of the sizes of paged_kv_serving_b200.design_bench")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_OBSTACLE, "context": reference_context()}))
@@ -516,6 +545,9 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design is not None:
+        print(json.dumps(run_design(args)))
+        return 0
     wanted = set() if args.skip_workloads else {w for w in args.workloads.split(",") if w}
     if "all" in wanted:
         wanted = {"mixed", "serve", "reference"}

@@ -1,0 +1,230 @@
+"""Prefill and decode throughput of one architecture at layer sizes of a real model (random
+weights), with the time of every kernel of a step against its roofline. ``bench.py --design``
+runs it for the Revupel design and, at equal sizes, for the Llama-style decoder.
+
+A step runs through ``ModelRunner.step``. For the kernel table one eager step is run with every
+kernel call of ``ops`` / ``ops.mixer_ops`` and every library product bracketed by CUDA events on
+the launching stream; a kernel's roofline time is the larger of its bytes over the measured copy
+bandwidth (its tensor arguments and results, or for attention the cache it must read) and its
+flops over the measured matrix peak.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+__all__ = ["SIZES", "llama_like", "measure", "revupel_config"]
+
+#: name -> sizes of a Revupel model whose layers resemble a served model's (latent attention of
+#: the kind with a compressed cache, an mLSTM block, eight experts of which two run, a dense block)
+SIZES = {
+    "1b": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=256, m_heads=4, m_dim=256,
+               m_vdim=512, ff=8192, experts=8, top=2, expert_ff=2048, shared_ff=2048, vocab=32000, side=64, pairs=2),
+    "7b": dict(width=4096, heads=32, dim=128, rot_dim=64, vdim=128, q_rank=1536, kv_rank=512, m_heads=8, m_dim=256,
+               m_vdim=512, ff=14336, experts=8, top=2, expert_ff=3584, shared_ff=3584, vocab=32000, side=64, pairs=2),
+}
+
+
+def revupel_config(size: str) -> dict:
+    z = SIZES[size]
+    attention = {"type": "latent_attention", "mixer": {
+        "heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["vdim"], "q_rank": z["q_rank"],
+        "kv_rank": z["kv_rank"], "scale": (z["dim"] + z["rot_dim"]) ** -0.5, "rot": {"base": 10000.0, "dims": z["rot_dim"]}}}
+    recurrent = {"type": "mlstm", "mixer": {"heads": z["m_heads"], "dim": z["m_dim"], "vdim": z["m_vdim"], "gate_cap": 15.0}}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared_ff"]}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    layers = []
+    for _ in range(z["pairs"]):
+        layers += [{**attention, "mlp": moe}, {**recurrent, "mlp": dense}]
+    return {"architecture": "Revupel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "canon": {"taps": 4},
+            "token_side": {"dim": z["side"]}, "layers": layers}
+
+
+def llama_like(size: str) -> dict:
+    """The Llama-style decoder at the same width, layer count and head count; its gated
+    feed-forward has the parameter count of the dense block above."""
+    z = SIZES[size]
+    return {"architecture": "LlamaToyDecoder", "vocab_size": z["vocab"], "d_model": z["width"], "n_layers": 2 * z["pairs"],
+            "n_heads": z["heads"], "n_kv_heads": max(1, z["heads"] // 4), "head_dim": 128, "d_ff": z["ff"] * 2 // 3 // 128 * 128,
+            "max_seq_len": 8192, "rope_theta": 10000.0, "norm_eps": 1e-6, "tie_embeddings": False}
+
+
+def _bytes_of(values) -> int:
+    return sum(v.numel() * v.element_size() for v in values if isinstance(v, torch.Tensor))
+
+
+class _KernelTimes:
+    """Brackets every kernel call of a step with CUDA events."""
+
+    def __init__(self, attention_cost) -> None:
+        self.records: list = []
+        self.attention_cost = attention_cost
+        self._undo: list = []
+
+    def _wrap(self, owner, name, kind):
+        original = getattr(owner, name)
+
+        def timed(*args, **kwargs):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            out = original(*args, **kwargs)
+            stop.record()
+            outs = out if isinstance(out, (tuple, list)) else (out,)
+            moved, flops = _bytes_of(args) + _bytes_of(outs), 0.0
+            if kind == "product":
+                a, b = args[0], args[1]
+                flops = 2.0 * a.numel() * b.shape[-1]
+            elif name in self.attention_cost:
+                moved, flops = self.attention_cost[name](args, out)
+            self.records.append((name, start, stop, moved, flops))
+            return out
+
+        setattr(owner, name, timed)
+        self._undo.append((owner, name, original))
+
+    def __enter__(self):
+        from paged_kv_serving_b200 import ops
+        from paged_kv_serving_b200.ops import gemm, mixer_ops
+
+        for name in ("embedding_gather", "add_rmsnorm", "silu_mul", "rope_kv_store", "attention_prefill_tcgen05",
+                     "attention_prefill_bf16", "attention_decode_tma", "attention_decode_flat", "attention_decode_bf16",
+                     "gemm_small_m", "gemm_tcgen05", "finish_norm"):
+            self._wrap(ops, name, "kernel")
+        for name in ("bias_act", "residual_add", "act_times_table", "route_top", "expert_act", "conv_residual", "mlstm",
+                     "latent_prepare", "latent_attention", "latent_attention_mma"):
+            self._wrap(mixer_ops, name, "kernel")
+        self._wrap(gemm, "matmul", "product")
+        self._wrap(torch, "bmm", "product")
+        return self
+
+    def __exit__(self, *exc):
+        for owner, name, original in reversed(self._undo):
+            setattr(owner, name, original)
+
+    def table(self, peaks: dict) -> dict:
+        torch.cuda.synchronize()
+        out: dict = {}
+        for name, start, stop, moved, flops in self.records:
+            row = out.setdefault(name, {"calls": 0, "ms": 0.0, "roofline_ms": 0.0})
+            row["calls"] += 1
+            row["ms"] += start.elapsed_time(stop)
+            row["roofline_ms"] += 1e3 * max(moved / (peaks["hbm_gbs"] * 1e9), flops / (peaks["bf16_tflops"] * 1e12))
+        for row in out.values():
+            row["of_roofline"] = round(row["roofline_ms"] / row["ms"], 4) if row["ms"] > 0 else None
+            row["ms"], row["roofline_ms"] = round(row["ms"], 4), round(row["roofline_ms"], 4)
+        return out
+
+
+def measure(config: dict, peaks: dict, *, prefill_tokens: int = 2048, batch: int = 8, context: int = 1024, steps: int = 32,
+            warmup: int = 4) -> dict:
+    """Prefill (one prompt in one step) and decode (``batch`` requests with ``context`` cached
+    tokens, one token each a step, captured graph) of a random-weights model of ``config``."""
+    from paged_kv_serving_b200.config import registry
+    from paged_kv_serving_b200.engine.batch import BatchEntry, ExecutionBatch
+    from paged_kv_serving_b200.engine.runner import ModelRunner
+    from paged_kv_serving_b200.models.decoder import DecoderModel
+
+    arch = registry.architecture(config["architecture"])
+    typed = getattr(arch, "config_class", None)
+    if typed is None:
+        from paged_kv_serving_b200.config import ModelConfig as typed
+    model = DecoderModel.from_random(typed.from_dict(config), seed=0, dtype="bfloat16", device="cuda:0")
+    block = 16
+    room = warmup + steps + 8
+    pages_per_seq = -(-(context + 2 * room + 64) // block)
+    prefill_pages = -(-prefill_tokens // block)
+    runner = ModelRunner(model, num_blocks=batch * pages_per_seq + prefill_pages, block_size=block, max_running_seqs=batch + 1)
+    groups = len(runner.groups)
+    rng = np.random.default_rng(0)
+    vocab = model.layout.vocab_size
+    has_state = runner.num_state_slots > 0
+
+    def entry(name, ids, first, table, want, slot):
+        return BatchEntry(name, tuple(int(t) for t in ids), first, tuple(table for _ in range(groups)), want,
+                          slot if has_state else None)
+
+    def timed(fn, repeat):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for i in range(repeat):
+            fn(i)
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / repeat
+
+    # attention's algorithmic cost, from the sizes of the step at hand
+    cost = {}
+    shape = {"tokens": 0, "keys": 0.0}
+
+    def latent_cost(args, out):
+        heads, rank = out.shape[0], out.shape[2]
+        dk = args[4].shape[-1]
+        flops = 2.0 * heads * shape["keys"] * (dk + rank)
+        moved = shape["cache_tokens"] * dk * 2 + _bytes_of((args[0], out))
+        return moved, flops
+
+    def llama_prefill_cost(args, out):
+        heads, hd = args[9], args[11]
+        return _bytes_of((args[0], out)), 4.0 * heads * hd * shape["keys"]
+
+    def llama_decode_cost(args, out):
+        kv, hd = args[10], args[11]
+        return shape["cache_tokens"] * kv * hd * 2 * 2 + _bytes_of((args[0], out)), 4.0 * args[9] * hd * shape["keys"]
+
+    def mlstm_cost(args, out):
+        heads, dim, vdim = args[13], args[14], args[15]
+        return _bytes_of((args[0], out)) * 2, 4.0 * args[0].shape[0] * heads * dim * vdim
+
+    cost.update({"latent_attention": latent_cost, "latent_attention_mma": latent_cost,
+                 "attention_prefill_tcgen05": llama_prefill_cost, "attention_prefill_bf16": llama_prefill_cost,
+                 "attention_decode_tma": llama_decode_cost, "attention_decode_flat": llama_decode_cost,
+                 "attention_decode_bf16": llama_decode_cost, "mlstm": mlstm_cost})
+
+    # ---- prefill ---------------------------------------------------------------------------------
+    table = tuple(range(batch * pages_per_seq, batch * pages_per_seq + prefill_pages))
+    prompt = rng.integers(0, vocab, size=prefill_tokens)
+    prefill_batch = ExecutionBatch((entry("p", prompt, 0, table, (prefill_tokens - 1,), batch),))
+    for _ in range(3):
+        runner.step(prefill_batch, clear_state_slots=[batch] if has_state else None)
+    prefill_ms = timed(lambda i: runner.step(prefill_batch, clear_state_slots=[batch] if has_state else None), 3)
+    shape.update(tokens=prefill_tokens, keys=prefill_tokens * (prefill_tokens + 1) / 2.0, cache_tokens=prefill_tokens)
+    with _KernelTimes(cost) as times:
+        runner.step(prefill_batch, clear_state_slots=[batch] if has_state else None)
+    prefill_kernels = times.table(peaks)
+
+    # ---- decode ----------------------------------------------------------------------------------
+    tables = [tuple(j * batch + i for j in range(pages_per_seq)) for i in range(batch)]
+    ids = rng.integers(0, vocab, size=(batch, context + 2 * room + 64))
+    for i in range(batch):
+        runner.step(ExecutionBatch((entry(f"s{i}", ids[i, :context], 0, tables[i], (), i),)),
+                    clear_state_slots=[i] if has_state else None)
+
+    def one(k, offset=0):
+        position = context + offset + k
+        runner.step(ExecutionBatch(tuple(entry(f"s{i}", (ids[i, position],), position, tables[i], (0,), i)
+                                         for i in range(batch))))
+
+    for k in range(warmup):
+        one(k)
+    decode_ms = timed(lambda k: one(k, warmup), steps)
+    position = context + warmup + steps
+    shape.update(tokens=batch, keys=float(batch * (position + 1)), cache_tokens=batch * (position + 1))
+    runner.use_graphs = False
+    with _KernelTimes(cost) as times:
+        one(0, warmup + steps)
+    decode_kernels = times.table(peaks)
+    weight_bytes = model.weight_bytes_read_per_step()
+    cache_bytes_per_token = sum((2 if g.values else 1) * len(g.entries) * g.n_kv_heads * g.head_dim * 2 for g in runner.groups)
+    step_bytes = weight_bytes + batch * position * cache_bytes_per_token
+    return {
+        "parameters": model.layout.parameter_count(),
+        "prefill": {"tokens": prefill_tokens, "ms": round(prefill_ms, 3), "tok_s": round(prefill_tokens / (prefill_ms / 1e3)),
+                    "kernels": prefill_kernels},
+        "decode": {"batch": batch, "context": context, "ms_per_step": round(decode_ms, 4),
+                   "tok_s": round(batch / (decode_ms / 1e3)), "step_bytes": step_bytes,
+                   "of_copy_bandwidth": round(step_bytes / (decode_ms / 1e3) / 1e9 / peaks["hbm_gbs"], 4),
+                   "kernels_eager": decode_kernels},
+    }

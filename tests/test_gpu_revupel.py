@@ -121,16 +121,24 @@ def tokens_for(config, count, seed):
 
 def close(got, want, dtype, what):
     """Rows of logits against the plain ones: the gap with its mean taken off, as a share of the
-    spread of the plain logits; float32 to 1e-4, bfloat16 to 4 %."""
+    spread of the plain logits. float32: every row within 1e-4. bfloat16: rounding moves a row by
+    about half a percent, but where two experts' router scores nearly tie it may pick the other one
+    and move that token's row by far more; so the typical row must stay within 1.5 %, at most one
+    row in sixteen may exceed 4 %, and none 30 % (a wrong key, page or state moves every row after it)."""
     got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
     assert got.shape == want.shape, f"{what}: shapes {got.shape} and {want.shape}"
     gap = got - want
     gap = gap - gap.mean(axis=-1, keepdims=True)
     spread = max(float(want.std()), 1e-6)
     error = np.sqrt((gap ** 2).mean(axis=-1)) / spread
-    bound = 1e-4 if dtype == "float32" else 4e-2
     assert np.isfinite(got).all(), f"{what}: the engine's logits are not finite"
-    assert float(error.max()) <= bound, f"{what}: row {int(error.argmax())} is off by {error.max():.3e} of the spread (bound {bound})"
+    worst = f"{what}: row {int(error.argmax())} is off by {error.max():.3e} of the spread"
+    if dtype == "float32":
+        assert float(error.max()) <= 1e-4, worst
+    else:
+        assert float(np.median(error)) <= 0.015, f"{what}: the typical row is off by {np.median(error):.3e} of the spread"
+        assert float(np.mean(error > 0.04)) <= 1 / 16 + 1e-9 or error.size < 16 and int((error > 0.04).sum()) <= 1, worst
+        assert float(error.max()) <= 0.3, worst
 
 
 def plain_logits(config, tensors, tokens):
