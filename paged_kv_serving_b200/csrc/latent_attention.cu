@@ -200,8 +200,8 @@ latent_attention_kernel(const Q* __restrict__ q_lat, const A* __restrict__ q_rot
 
 
 // ---------------------------------------------------------------------------------------------
-// The tensor-core form for bfloat16: one block of 4 warps per 64 consecutive rows of an entry
-// (each warp 16 rows), keys in tiles of 32 absolute positions aligned to multiples of 32 from
+// The tensor-core form for bfloat16: one block of 8 warps per 128 consecutive rows of an entry
+// (each warp 16 rows; 4 warps and 64 rows where the larger block's shared memory does not fit), keys in tiles of 32 absolute positions aligned to multiples of 32 from
 // position 0, double-buffered with cp.async from the pages the block table names. S = Q K^T and
 // O += P V run on mma.sync m16n8k16 with float32 accumulators; the values of a tile are the
 // first `rank` columns of its keys, read from the same shared-memory tile (transposed loads).
@@ -209,10 +209,9 @@ latent_attention_kernel(const Q* __restrict__ q_lat, const A* __restrict__ q_rot
 // rank > VT and each computes the scores again). Scores, maxima, sums and exponentials are
 // float32; queries and probabilities enter the products as bfloat16.
 // ---------------------------------------------------------------------------------------------
-constexpr int LM_BM = 64;
 constexpr int LM_BN = 32;
-constexpr int LM_THREADS = 128;
 constexpr int LM_PAD = 8;
+constexpr size_t LM_SMEM_LIMIT = 200 * 1024;
 
 __device__ __forceinline__ uint32_t lm_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void lm_cp_async16(void* smem, const void* gmem) {
@@ -258,6 +257,7 @@ struct LatentParams {
   int* status;
 };
 
+template <int LM_THREADS>
 __device__ __forceinline__ void lm_load_tile(bf16* tile, const LatentParams& p, const int32_t* table, int base, int key_lo,
                                              int key_hi, int dk, int ld) {
   const int chunks = dk >> 3;
@@ -274,9 +274,11 @@ __device__ __forceinline__ void lm_load_tile(bf16* tile, const LatentParams& p, 
   }
 }
 
-template <int VT, typename Q>
-__global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(const LatentParams p) {
+template <int VT, typename Q, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) latent_attention_mma_kernel(const LatentParams p) {
   constexpr int DTILES = VT / 8;
+  constexpr int LM_BM = WARPS * 16;
+  constexpr int LM_THREADS = WARPS * 32;
   extern __shared__ __align__(16) unsigned char lm_smem[];
   const int dk = p.rank + p.rot;
   const int ld = dk + LM_PAD;
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(const 
   const int tile_begin = key_lo / LM_BN, tile_end = (key_hi - 1) / LM_BN;     // inclusive
   const int32_t* table = p.block_table + (size_t)s * p.table_stride;
 
-  lm_load_tile(k_s, p, table, tile_begin * LM_BN, key_lo, key_hi, dk, ld);
+  lm_load_tile<LM_THREADS>(k_s, p, table, tile_begin * LM_BN, key_lo, key_hi, dk, ld);
   lm_cp_async_commit();
 
   // the queries of this block: absorbed part as it is, rotated part rotated by the row's position
@@ -353,7 +355,7 @@ __global__ void __launch_bounds__(LM_THREADS) latent_attention_mma_kernel(const 
     const int stage = (tile - tile_begin) & 1;
     const int base = tile * LM_BN;
     if (tile < tile_end) {
-      lm_load_tile(k_s + (stage ^ 1) * LM_BN * ld, p, table, base + LM_BN, key_lo, key_hi, dk, ld);
+      lm_load_tile<LM_THREADS>(k_s + (stage ^ 1) * LM_BN * ld, p, table, base + LM_BN, key_lo, key_hi, dk, ld);
       lm_cp_async_commit();
       lm_cp_async_wait<1>();
     } else {
@@ -530,27 +532,31 @@ PKV_EXPORT int pkv_latent_attention(const void* q_lat, int q_lat_dtype, const vo
   return PKV_ERR_DTYPE;
 }
 
-PKV_EXPORT int pkv_latent_mma_rows_per_block() { return LM_BM; }
+static size_t lm_smem_bytes(int rank, int rot, int warps) {
+  return (size_t)(warps * 16 + 2 * LM_BN) * (rank + rot + LM_PAD) * sizeof(bf16);
+}
 
 // Whether the tensor-core kernel takes these sizes (else the general kernel above serves them).
 PKV_EXPORT int pkv_latent_mma_supports(int rank, int rot) {
-  const int dk = rank + rot;
-  if (rank < 16 || (rank & 15) || (dk & 15)) return 0;
-  const size_t smem = (size_t)(LM_BM + 2 * LM_BN) * (dk + LM_PAD) * sizeof(bf16);
-  return smem <= 200 * 1024 ? 1 : 0;
+  if (rank < 16 || (rank & 15) || ((rank + rot) & 15)) return 0;
+  return lm_smem_bytes(rank, rot, 4) <= LM_SMEM_LIMIT ? 1 : 0;
 }
 
-template <int VT, typename Q>
+// Rows of a block for these sizes (the host's work list is cut to it).
+PKV_EXPORT int pkv_latent_mma_rows_per_block(int rank, int rot) {
+  return lm_smem_bytes(rank, rot, 8) <= LM_SMEM_LIMIT ? 128 : 64;
+}
+
+template <int VT, typename Q, int WARPS>
 static int launch_latent_mma(const LatentParams& p, int n_work, cudaStream_t s) {
-  const int dk = p.rank + p.rot;
-  const size_t smem = (size_t)(LM_BM + 2 * LM_BN) * (dk + LM_PAD) * sizeof(bf16);
+  const size_t smem = lm_smem_bytes(p.rank, p.rot, WARPS);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<VT, Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(latent_attention_mma_kernel<VT, Q, WARPS>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(n_work, (p.rank + VT - 1) / VT);
-  latent_attention_mma_kernel<VT, Q><<<grid, LM_THREADS, smem, s>>>(p);
+  latent_attention_mma_kernel<VT, Q, WARPS><<<grid, WARPS * 32, smem, s>>>(p);
   return launch_status();
 }
 
@@ -573,11 +579,14 @@ PKV_EXPORT int pkv_latent_attention_mma(const void* q_lat, int q_lat_dtype, cons
   p.page_size = page_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.num_pages = num_pages;
   p.status = status;
   cudaStream_t s = (cudaStream_t)stream;
-#define PKV_LM(VT)                                                             \
-  do {                                                                         \
-    if (q_lat_dtype == PKV_F32) return launch_latent_mma<VT, float>(p, n_work, s); \
-    if (q_lat_dtype == PKV_BF16) return launch_latent_mma<VT, bf16>(p, n_work, s); \
-    return PKV_ERR_DTYPE;                                                      \
+  const bool wide = pkv_latent_mma_rows_per_block(rank, rot) == 128;
+#define PKV_LM(VT)                                                                                  \
+  do {                                                                                              \
+    if (q_lat_dtype == PKV_F32 && wide) return launch_latent_mma<VT, float, 8>(p, n_work, s);      \
+    if (q_lat_dtype == PKV_F32) return launch_latent_mma<VT, float, 4>(p, n_work, s);              \
+    if (q_lat_dtype == PKV_BF16 && wide) return launch_latent_mma<VT, bf16, 8>(p, n_work, s);      \
+    if (q_lat_dtype == PKV_BF16) return launch_latent_mma<VT, bf16, 4>(p, n_work, s);              \
+    return PKV_ERR_DTYPE;                                                                           \
   } while (0)
   if (rank <= 64) PKV_LM(64);
   if (rank <= 128) PKV_LM(128);

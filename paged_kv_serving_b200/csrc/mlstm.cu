@@ -7,19 +7,22 @@
 //   o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
 // Everything here is float32: the projections arrive as float32, the state is float32.
 //
-// Three kernels. `gates`: one warp per (entry, head) walks the tokens, keeps n in registers
-// (dimension d on lane d % 32) and m, and leaves a_t, b_t and the denominator per (token, head).
-// `scan`: the columns of S are independent given those three numbers; a group of P lanes owns
-// one column (each lane R of its `dim` entries), so a block of 128 threads owns 128 / P columns
-// and the grid is (column slices, heads, entries). The order of operations per token does not
-// depend on how the sequence was cut into portions, so a portion boundary changes nothing.
-// `finish`: per (token, head) the output is divided by its root mean square, multiplied by the
-// norm's weight and by sigmoid of the output gate's pre-activation.
+// Three kernels.
+// `gates`: one warp per (entry, head). The recurrence of m is a chain of maps x -> max(x + f, i),
+// which compose associatively ((f1, i1) then (f2, i2) is (f1 + f2, max(i1 + f2, i2))): the warp
+// takes 32 tokens at a time, one per lane (the gates' transcendentals run side by side), scans the
+// maps with shuffles, and leaves a_t, b_t and m_t per (token, head).
+// `scan`: given a_t and b_t the columns of S are independent, and n is one more column whose
+// value is always 1. A group of P lanes owns one column (each lane R of its `dim` entries), a
+// block of 128 threads owns 128 / P columns, the grid is (column slices, heads, entries). Keys,
+// queries, values and coefficients of a few tokens at a time arrive in shared memory by cp.async,
+// the next chunk while this one is walked. The order of operations per token and column does not
+// depend on how the sequence was cut into portions.
+// `finish`: per (token, head) the numerators are divided by the denominator, then by their root
+// mean square, multiplied by the norm's weight and by sigmoid of the output gate's pre-activation.
 #include "common.cuh"
 
 namespace pkv {
-
-constexpr int MLSTM_MAX_N = 32;     // dim <= 32 * MLSTM_MAX_N for the gates kernel
 
 __device__ __forceinline__ float log_sigmoid(float z) {
   // log(1 / (1 + exp(-z))) without overflow on either side
@@ -27,103 +30,151 @@ __device__ __forceinline__ float log_sigmoid(float z) {
 }
 
 __global__ void __launch_bounds__(32)
-mlstm_gates_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int i_off, int f_off,
-                   const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale,
-                   float* __restrict__ n_state, float* __restrict__ m_state, const int32_t* __restrict__ seq_starts,
-                   const int32_t* __restrict__ state_slots, float* __restrict__ coef, int heads, int dim) {
+mlstm_gates_kernel(const float* __restrict__ proj, int ld, int i_off, int f_off, const float* __restrict__ i_bias,
+                   const float* __restrict__ f_bias, float cap, float* __restrict__ m_state,
+                   const int32_t* __restrict__ seq_starts, const int32_t* __restrict__ state_slots,
+                   float* __restrict__ coef, int heads) {
   const int head = blockIdx.x, s = blockIdx.y, lane = threadIdx.x;
   const int start = seq_starts[s], count = seq_starts[s + 1] - start;
-  const int slot = state_slots[s];
-  float* n_mine = n_state + ((size_t)slot * heads + head) * dim;
-  float* m_mine = m_state + (size_t)slot * heads + head;
-  float n[MLSTM_MAX_N];
-#pragma unroll
-  for (int r = 0; r < MLSTM_MAX_N; ++r) {
-    const int d = lane + 32 * r;
-    n[r] = d < dim ? n_mine[d] : 0.0f;
-  }
-  float m = *m_mine;
+  float* m_mine = m_state + (size_t)state_slots[s] * heads + head;
+  float m_in = *m_mine;
   const float bi = i_bias[head], bf = f_bias[head];
-  for (int j = 0; j < count; ++j) {
-    const float* row = proj + (size_t)(start + j) * ld;
-    const float log_i = cap * tanhf((row[i_off + head] + bi) / cap);
-    const float log_f = log_sigmoid(cap * tanhf((row[f_off + head] + bf) / cap));
-    const float m_new = fmaxf(log_f + m, log_i);
-    const float a = expf(log_f + m - m_new), b = expf(log_i - m_new);
-    float dot = 0.0f;
+  for (int base = 0; base < count; base += 32) {
+    const int j = base + lane;
+    const bool live = j < count;
+    float log_i = -INFINITY, log_f = 0.0f;              // the identity map for lanes past the end
+    if (live) {
+      const float* row = proj + (size_t)(start + j) * ld;
+      log_i = cap * tanhf((row[i_off + head] + bi) / cap);
+      log_f = log_sigmoid(cap * tanhf((row[f_off + head] + bf) / cap));
+    }
+    // inclusive scan of the maps x -> max(x + F, M)
+    float F = log_f, M = log_i;
 #pragma unroll
-    for (int r = 0; r < MLSTM_MAX_N; ++r) {
-      const int d = lane + 32 * r;
-      if (d < dim) {
-        n[r] = a * n[r] + b * row[k_off + head * dim + d];
-        dot = fmaf(n[r], row[q_off + head * dim + d] * q_scale, dot);
+    for (int d = 1; d < 32; d <<= 1) {
+      const float f_before = __shfl_up_sync(0xffffffffu, F, d), m_before = __shfl_up_sync(0xffffffffu, M, d);
+      if (lane >= d) {
+        M = fmaxf(m_before + F, M);
+        F = f_before + F;
       }
     }
-    dot = warp_sum(dot);
-    m = m_new;
-    if (lane == 0) {
+    const float m_t = fmaxf(m_in + F, M);
+    float m_prev = __shfl_up_sync(0xffffffffu, m_t, 1);
+    if (lane == 0) m_prev = m_in;
+    if (live) {
       float* c = coef + ((size_t)(start + j) * heads + head) * 4;
-      c[0] = a;
-      c[1] = b;
-      c[2] = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
+      c[0] = expf(log_f + m_prev - m_t);
+      c[1] = expf(log_i - m_t);
+      c[2] = m_t;
     }
+    m_in = __shfl_sync(0xffffffffu, m_t, 31);
   }
-#pragma unroll
-  for (int r = 0; r < MLSTM_MAX_N; ++r) {
-    const int d = lane + 32 * r;
-    if (d < dim) n_mine[d] = n[r];
-  }
-  if (lane == 0) *m_mine = m;
+  if (lane == 0) *m_mine = m_in;
 }
 
+__device__ __forceinline__ void ml_cp_async4(float* smem, const float* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void ml_cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void ml_cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
 // P lanes per column, R entries of the column per lane: P * R >= dim, P a power of two <= 32.
+// Column `vdim` is the normaliser n (its value is 1 for every token; its state lives in n_state and
+// its readout n . q goes to `dots`).
 template <int R>
 __global__ void __launch_bounds__(128)
 mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, float q_scale,
-                  const float* __restrict__ coef, float* __restrict__ s_state, const int32_t* __restrict__ seq_starts,
-                  const int32_t* __restrict__ state_slots, float* __restrict__ out, int heads, int dim, int vdim, int P) {
+                  const float* __restrict__ coef, float* __restrict__ s_state, float* __restrict__ n_state,
+                  const int32_t* __restrict__ seq_starts, const int32_t* __restrict__ state_slots,
+                  float* __restrict__ out, float* __restrict__ dots, int heads, int dim, int vdim, int P, int chunk) {
+  extern __shared__ float ml_smem[];
   const int head = blockIdx.y, s = blockIdx.z;
   const int per_block = 128 / P;
-  const int column = blockIdx.x * per_block + threadIdx.x / P;
+  const int c0 = blockIdx.x * per_block;
+  const int column = c0 + threadIdx.x / P;
   const int p = threadIdx.x % P;
-  const bool live = column < vdim;
+  const bool live = column <= vdim;
+  const bool is_n = column == vdim;
   const int start = seq_starts[s], count = seq_starts[s + 1] - start;
   const int slot = state_slots[s];
-  // S is [dim][vdim] per (slot, head)
-  float* s_mine = s_state + ((size_t)slot * heads + head) * dim * vdim + (live ? column : 0);
+  // one stage of shared memory: k [chunk][dim], q [chunk][dim], v [chunk][per_block], (a, b) [chunk][2]
+  const int stage_floats = chunk * (2 * dim + per_block + 2);
+  float* mine = is_n ? n_state + ((size_t)slot * heads + head) * dim
+                     : s_state + ((size_t)slot * heads + head) * dim * vdim + (live ? column : 0);
+  const size_t stride = is_n ? 1 : (size_t)vdim;
   float sv[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int d = p + P * r;
-    sv[r] = (live && d < dim) ? s_mine[(size_t)d * vdim] : 0.0f;
+    sv[r] = (live && d < dim) ? mine[(size_t)d * stride] : 0.0f;
   }
-  for (int j = 0; j < count; ++j) {
-    const float* row = proj + (size_t)(start + j) * ld;
-    const float* c = coef + ((size_t)(start + j) * heads + head) * 4;
-    const float a = c[0], b = c[1], denom = c[2];
-    const float bv = live ? b * row[v_off + head * vdim + column] : 0.0f;
-    float num = 0.0f;
+
+  auto load = [&](int stage, int first) {
+    float* ks = ml_smem + stage * stage_floats;
+    float* qs = ks + chunk * dim;
+    float* vs = qs + chunk * dim;
+    float* cs = vs + chunk * per_block;
+    const int n = min(chunk, count - first);
+    for (int idx = threadIdx.x; idx < n * dim; idx += 128) {
+      const int t = idx / dim, d = idx - t * dim;
+      const float* row = proj + (size_t)(start + first + t) * ld;
+      ml_cp_async4(ks + idx, row + k_off + head * dim + d);
+      ml_cp_async4(qs + idx, row + q_off + head * dim + d);
+    }
+    for (int idx = threadIdx.x; idx < n * per_block; idx += 128) {
+      const int t = idx / per_block, c = idx - t * per_block;
+      if (c0 + c < vdim) ml_cp_async4(vs + idx, proj + (size_t)(start + first + t) * ld + v_off + head * vdim + c0 + c);
+    }
+    for (int idx = threadIdx.x; idx < n * 2; idx += 128)
+      ml_cp_async4(cs + idx, coef + ((size_t)(start + first + (idx >> 1)) * heads + head) * 4 + (idx & 1));
+  };
+
+  if (count > 0) load(0, 0);
+  ml_cp_async_commit();
+  int stage = 0;
+  for (int first = 0; first < count; first += chunk, stage ^= 1) {
+    if (first + chunk < count) load(stage ^ 1, first + chunk);
+    ml_cp_async_commit();
+    ml_cp_async_wait<1>();
+    __syncthreads();
+    const float* ks = ml_smem + stage * stage_floats;
+    const float* qs = ks + chunk * dim;
+    const float* vs = qs + chunk * dim;
+    const float* cs = vs + chunk * per_block;
+    const int n = min(chunk, count - first);
+    for (int t = 0; t < n; ++t) {
+      const float a = cs[2 * t], b = cs[2 * t + 1];
+      const float bv = is_n ? b : (live ? b * vs[t * per_block + (column - c0)] : 0.0f);
+      float num = 0.0f;
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int d = p + P * r;
-      if (d < dim) {
-        sv[r] = fmaf(bv, row[k_off + head * dim + d], a * sv[r]);
-        num = fmaf(sv[r], row[q_off + head * dim + d] * q_scale, num);
+      for (int r = 0; r < R; ++r) {
+        const int d = p + P * r;
+        if (d < dim) {
+          sv[r] = fmaf(bv, ks[t * dim + d], a * sv[r]);
+          num = fmaf(sv[r], qs[t * dim + d], num);
+        }
+      }
+      for (int o = P >> 1; o > 0; o >>= 1) num += __shfl_xor_sync(0xffffffffu, num, o);
+      if (live && p == 0) {
+        const size_t token = (size_t)(start + first + t);
+        if (is_n) dots[token * heads + head] = num * q_scale;
+        else out[token * heads * vdim + head * vdim + column] = num * q_scale;
       }
     }
-    for (int o = P >> 1; o > 0; o >>= 1) num += __shfl_xor_sync(0xffffffffu, num, o);
-    if (live && p == 0) out[(size_t)(start + j) * heads * vdim + head * vdim + column] = num / denom;
+    __syncthreads();        // the stage is free for the load after next
   }
+  ml_cp_async_wait<0>();
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int d = p + P * r;
-    if (live && d < dim) s_mine[(size_t)d * vdim] = sv[r];
+    if (live && d < dim) mine[(size_t)d * stride] = sv[r];
   }
 }
 
 // One warp per (token, head): o / rms(o) * weight * sigmoid(gate)
 template <typename O>
-__global__ void mlstm_finish_kernel(const float* __restrict__ o, const float* __restrict__ weight,
+__global__ void mlstm_finish_kernel(const float* __restrict__ o, const float* __restrict__ dots,
+                                    const float* __restrict__ coef, const float* __restrict__ weight,
                                     const float* __restrict__ proj, int ld, int g_off, O* __restrict__ out,
                                     long long rows, int heads, int vdim, float eps) {
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -132,13 +183,17 @@ __global__ void mlstm_finish_kernel(const float* __restrict__ o, const float* __
   const long long t = row / heads;
   const int head = (int)(row - t * heads);
   const float* mine = o + (size_t)row * vdim;
+  const float denom = fmaxf(fabsf(dots[row]), expf(-coef[(size_t)row * 4 + 2])) + 1e-6f;
   float ss = 0.0f;
-  for (int c = lane; c < vdim; c += 32) ss = fmaf(mine[c], mine[c], ss);
+  for (int c = lane; c < vdim; c += 32) {
+    const float v = mine[c] / denom;
+    ss = fmaf(v, v, ss);
+  }
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
   for (int c = lane; c < vdim; c += 32) {
     const float gate = proj[(size_t)t * ld + g_off + head * vdim + c];
-    const float v = mine[c] * inv * weight[head * vdim + c] * (1.0f / (1.0f + expf(-gate)));
+    const float v = mine[c] / denom * inv * weight[head * vdim + c] * (1.0f / (1.0f + expf(-gate)));
     out[(size_t)row * vdim + c] = from_float<O>(v);
   }
 }
@@ -149,7 +204,8 @@ using namespace pkv;
 
 // proj: float32 [tokens, ld] with the columns of q, k ([heads][dim]), v, g ([heads][vdim]) and of
 // the two gates ([heads]) at the given offsets. coef: float32 scratch [tokens, heads, 4].
-// o: float32 scratch [tokens, heads * vdim]. out: [tokens, heads * vdim] in out_dtype.
+// o: float32 scratch [tokens, heads * vdim + heads] (numerators, then n . q per (token, head)).
+// out: [tokens, heads * vdim] in out_dtype.
 PKV_EXPORT int pkv_mlstm(const float* proj, int ld, int q_off, int k_off, int v_off, int g_off, int i_off, int f_off,
                          const float* i_bias, const float* f_bias, const float* norm_weight, float cap, float q_scale,
                          float eps, float* s_state, float* n_state, float* m_state, const int32_t* seq_starts,
@@ -157,28 +213,38 @@ PKV_EXPORT int pkv_mlstm(const float* proj, int ld, int q_off, int k_off, int v_
                          int seqs, int heads, int dim, int vdim, void* stream) {
   if (tokens <= 0 || seqs <= 0) return 0;
   if (heads < 1 || dim < 1 || vdim < 1 || !(cap > 0.0f)) return PKV_ERR_SIZE;
-  if (dim > 32 * MLSTM_MAX_N || seqs > 65535 || heads > 65535) return PKV_ERR_LIMIT;
+  if (dim > 1024 || seqs > 65535 || heads > 65535) return PKV_ERR_LIMIT;
   if (out_dtype != PKV_F32 && out_dtype != PKV_BF16) return PKV_ERR_DTYPE;
   cudaStream_t s = (cudaStream_t)stream;
-  mlstm_gates_kernel<<<dim3(heads, seqs), 32, 0, s>>>(proj, ld, q_off, k_off, i_off, f_off, i_bias, f_bias, cap, q_scale,
-                                                     n_state, m_state, seq_starts, state_slots, coef, heads, dim);
+  mlstm_gates_kernel<<<dim3(heads, seqs), 32, 0, s>>>(proj, ld, i_off, f_off, i_bias, f_bias, cap, m_state, seq_starts,
+                                                     state_slots, coef, heads);
   // lanes per column: enough that a lane holds at most R entries of it
-  int R = dim <= 256 ? 8 : 32;
+  const int R = dim <= 256 ? 8 : 32;
   int P = 1;
   while (P * R < dim) P <<= 1;
   const int per_block = 128 / P;
-  dim3 grid((vdim + per_block - 1) / per_block, heads, seqs);
-  if (R == 8)
-    mlstm_scan_kernel<8><<<grid, 128, 0, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, seq_starts, state_slots,
-                                              o, heads, dim, vdim, P);
-  else
-    mlstm_scan_kernel<32><<<grid, 128, 0, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, seq_starts,
-                                               state_slots, o, heads, dim, vdim, P);
+  // tokens per stage of shared memory: as many as fit in about 40 KB a stage, 16 at most
+  int chunk = 16;
+  while (chunk > 1 && (size_t)chunk * (2 * dim + per_block + 2) * sizeof(float) > 40 * 1024) chunk >>= 1;
+  const size_t smem = 2 * (size_t)chunk * (2 * dim + per_block + 2) * sizeof(float);
+  float* dots = o + (size_t)tokens * heads * vdim;
+  dim3 grid((vdim + 1 + per_block - 1) / per_block, heads, seqs);
+  if (R == 8) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_scan_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    mlstm_scan_kernel<8><<<grid, 128, smem, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, n_state, seq_starts,
+                                                 state_slots, o, dots, heads, dim, vdim, P, chunk);
+  } else {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    mlstm_scan_kernel<32><<<grid, 128, smem, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, n_state, seq_starts,
+                                                  state_slots, o, dots, heads, dim, vdim, P, chunk);
+  }
   const long long rows = (long long)tokens * heads;
   const unsigned blocks = (unsigned)((rows + 3) / 4);
   if (out_dtype == PKV_F32)
-    mlstm_finish_kernel<float><<<blocks, 128, 0, s>>>(o, norm_weight, proj, ld, g_off, (float*)out, rows, heads, vdim, eps);
+    mlstm_finish_kernel<float><<<blocks, 128, 0, s>>>(o, dots, coef, norm_weight, proj, ld, g_off, (float*)out, rows, heads,
+                                                      vdim, eps);
   else
-    mlstm_finish_kernel<bf16><<<blocks, 128, 0, s>>>(o, norm_weight, proj, ld, g_off, (bf16*)out, rows, heads, vdim, eps);
+    mlstm_finish_kernel<bf16><<<blocks, 128, 0, s>>>(o, dots, coef, norm_weight, proj, ld, g_off, (bf16*)out, rows, heads,
+                                                     vdim, eps);
   return launch_status();
 }

@@ -112,6 +112,66 @@ __global__ void expert_act_kernel(const X* __restrict__ up, int ld, const float*
   out[(size_t)t * cols + c] = from_float<X>(v);
 }
 
+
+// --- 16-byte forms for bfloat16 rows whose sizes are multiples of 8 -------------------------------
+
+struct Pack8 { float v[8]; };
+
+__device__ __forceinline__ Pack8 load8(const bf16* p) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  Pack8 out;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    out.v[2 * i] = f.x;
+    out.v[2 * i + 1] = f.y;
+  }
+  return out;
+}
+
+__device__ __forceinline__ void store8(bf16* p, const Pack8& x) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(x.v[2 * i], x.v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+__global__ void bias_act_bf16x8_kernel(const bf16* __restrict__ x, const float* __restrict__ bias, bf16* __restrict__ out,
+                                       long long groups, int cols, int act) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= groups) return;
+  Pack8 v = load8(x + i * 8);
+  const int c = (int)((i * 8) % cols);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v.v[k] = activate(v.v[k] + (bias ? bias[c + k] : 0.0f), act);
+  store8(out + i * 8, v);
+}
+
+__global__ void expert_act_bf16x8_kernel(const bf16* __restrict__ up, int ld, const float* __restrict__ weights,
+                                         const float* __restrict__ gate, int gate_ld, bf16* __restrict__ out, int tokens,
+                                         int experts, int ff, int shared_ff, int act) {
+  const int cols = experts * ff + shared_ff;
+  const int per_row = cols >> 3;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * per_row) return;
+  const int t = (int)(i / per_row), c = (int)(i - (long long)t * per_row) << 3;
+  float scale;
+  if (c < experts * ff) scale = weights[(size_t)t * experts + c / ff];
+  else scale = gate ? 1.0f / (1.0f + expf(-gate[(size_t)t * gate_ld])) : 1.0f;
+  Pack8 v;
+  if (scale != 0.0f) {
+    v = load8(up + (size_t)t * ld + c);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v.v[k] = scale * activate(v.v[k], act);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v.v[k] = 0.0f;
+  }
+  store8(out + (size_t)t * cols + c, v);
+}
+
 }  // namespace pkv
 
 using namespace pkv;
@@ -124,6 +184,10 @@ PKV_EXPORT int pkv_bias_act(const void* x, int x_dtype, const float* bias, void*
   if (total <= 0) return 0;
   if (act < 0 || act > 4) return PKV_ERR_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
+  if (x_dtype == PKV_BF16 && out_dtype == PKV_BF16 && cols % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    bias_act_bf16x8_kernel<<<blocks_for(total / 8, 256), 256, 0, s>>>((const bf16*)x, bias, (bf16*)out, total / 8, cols, act);
+    return launch_status();
+  }
 #define PKV_BA(X, O) bias_act_kernel<X, O><<<blocks_for(total, 256), 256, 0, s>>>((const X*)x, bias, (O*)out, total, cols, act); return launch_status()
   if (x_dtype == PKV_F32 && out_dtype == PKV_F32) { PKV_BA(float, float); }
   if (x_dtype == PKV_F32 && out_dtype == PKV_BF16) { PKV_BA(float, bf16); }
@@ -182,6 +246,10 @@ PKV_EXPORT int pkv_expert_act(const void* up, int dtype, int ld, const float* we
   if (dtype == PKV_F32) {
     expert_act_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)up, ld, weights, gate, gate_ld,
                                                                     (float*)out, tokens, experts, ff, shared_ff, act);
+  } else if (dtype == PKV_BF16 && ff % 8 == 0 && shared_ff % 8 == 0 && ld % 8 == 0 && ((uintptr_t)up & 15) == 0 &&
+             ((uintptr_t)out & 15) == 0) {
+    expert_act_bf16x8_kernel<<<blocks_for(total / 8, 256), 256, 0, s>>>((const bf16*)up, ld, weights, gate, gate_ld, (bf16*)out,
+                                                                         tokens, experts, ff, shared_ff, act);
   } else if (dtype == PKV_BF16) {
     expert_act_kernel<bf16><<<blocks_for(total, 256), 256, 0, s>>>((const bf16*)up, ld, weights, gate, gate_ld,
                                                                    (bf16*)out, tokens, experts, ff, shared_ff, act);

@@ -203,12 +203,14 @@ class ModelRunner:
                 raise ValueError(f"sequence {entry.seq_id}: token id outside the vocabulary")
             if entry.context_len > config.max_positions:
                 raise ValueError(f"sequence {entry.seq_id}: position beyond max_seq_len")
-            if len(entry.block_tables) != len(self.groups):
+            # (a model without paged keys, all its mixers keeping a state of their own, has no page
+            # group; the one empty table a sequence carries then is not looked at)
+            if len(entry.block_tables) != len(self.groups) and self.groups:
                 raise ValueError(f"sequence {entry.seq_id}: {len(entry.block_tables)} page tables for "
                                  f"{len(self.groups)} page groups")
             first_page = entry.first_position // self.block_size
             last_page = (entry.context_len - 1) // self.block_size
-            for table in entry.block_tables:
+            for table in entry.block_tables if self.groups else ():
                 if last_page >= len(table):
                     raise ValueError(f"sequence {entry.seq_id}: position {entry.context_len - 1} has no page in the table")
                 for page in table[first_page:last_page + 1]:

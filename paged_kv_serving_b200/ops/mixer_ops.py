@@ -152,7 +152,7 @@ def mlstm(proj: torch.Tensor, offsets: dict[str, int], i_bias: torch.Tensor, f_b
         raise ValueError("mlstm: a vector does not fit the head count")
     seqs = seq_starts.numel() - 1
     coef = _empty((tokens, heads, 4), torch.float32, proj.device)
-    o = _empty((tokens, heads * vdim), torch.float32, proj.device)
+    o = _empty((tokens * heads * (vdim + 1),), torch.float32, proj.device)     # numerators, then n . q per (token, head)
     out = _empty((tokens, heads * vdim), out_dtype, proj.device)
     fn = _fn("mlstm", "pkv_mlstm",
              [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float,
@@ -229,10 +229,12 @@ def latent_attention(q_lat: torch.Tensor, q: torch.Tensor, q_rot_offset: int, q_
     return out
 
 
-def latent_mma_rows_per_block() -> int:
+def latent_mma_rows_per_block(rank: int, rot: int) -> int:
+    """Rows of one block of the tensor-core kernel at these sizes (128, or 64 for wide latents)."""
     fn = ops.library("latent_attention").pkv_latent_mma_rows_per_block
     fn.restype = c_int
-    return int(fn())
+    fn.argtypes = [c_int, c_int]
+    return int(fn(int(rank), int(rot)))
 
 
 def latent_mma_supports(rank: int, rot: int) -> bool:
@@ -250,7 +252,7 @@ def latent_attention_mma(q_lat: torch.Tensor, q: torch.Tensor, q_rot_offset: int
                          rot: int, rot_dims: int, page_size: int, window: int, scale: float, status: torch.Tensor,
                          n_work: int | None = None) -> torch.Tensor:
     """``latent_attention`` on the tensor cores, for bfloat16 queries and cache (``q_lat`` float32
-    or bfloat16); the work list is in blocks of ``latent_mma_rows_per_block()`` rows."""
+    or bfloat16); the work list is in blocks of ``latent_mma_rows_per_block(rank, rot)`` rows."""
     _need(q_lat, None, "q_lat"); _need(q, torch.bfloat16, "q"); _need(pool, torch.bfloat16, "pool")
     tokens = q.shape[0]
     if q_lat.shape != (heads, tokens, rank):

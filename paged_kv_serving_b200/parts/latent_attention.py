@@ -96,21 +96,26 @@ class LatentAttention(Part):
         return self._mma_ok
 
     def _work_names(self, ctx: StepContext) -> tuple[str, str]:
-        kind = "mma" if self._tensor_cores(ctx) else "general"
+        # (everything the work list depends on is part of its name: layers share a list only when it is the same)
+        kind = f"mma{self.kv_rank}+{self.rot_dim}" if self._tensor_cores(ctx) else "general"
         return (f"latent_attention/{kind}/work_seq/h{self.heads}", f"latent_attention/{kind}/work_row0/h{self.heads}")
 
     def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
         seq_name, row_name = self._work_names(ctx)
         if seq_name in ctx.arena:
             return
-        per_block = mixer_ops.latent_mma_rows_per_block() if self._tensor_cores(ctx) else mixer_ops.latent_rows_per_block()
+        per_block = mixer_ops.latent_mma_rows_per_block(self.kv_rank, self.rot_dim) if self._tensor_cores(ctx) \
+            else mixer_ops.latent_rows_per_block()
         rows = np.asarray(ctx.seq_lens, dtype=np.int64) * self.heads
         blocks = (rows + per_block - 1) // per_block
         work_seq = np.repeat(np.arange(len(rows), dtype=np.int64), blocks)
         starts = np.cumsum(blocks) - blocks
         work_row0 = (np.arange(int(blocks.sum()), dtype=np.int64) - np.repeat(starts, blocks)) * per_block
-        ctx.arena.add(seq_name, work_seq)
-        ctx.arena.add(row_name, work_row0)
+        # the blocks with the most keys to walk first, so that the last round of blocks is short
+        cost = np.asarray(ctx.first_positions, dtype=np.int64)[work_seq] + work_row0 // self.heads
+        order = np.argsort(-cost, kind="stable")
+        ctx.arena.add(seq_name, work_seq[order])
+        ctx.arena.add(row_name, work_row0[order])
 
     def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding) -> torch.Tensor:
         group = ctx.groups[binding.group]
