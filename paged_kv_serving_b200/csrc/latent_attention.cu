@@ -211,7 +211,7 @@ latent_attention_kernel(const Q* __restrict__ q_lat, const A* __restrict__ q_rot
 // ---------------------------------------------------------------------------------------------
 constexpr int LM_BN = 32;
 constexpr int LM_PAD = 8;
-constexpr size_t LM_SMEM_LIMIT = 200 * 1024;
+constexpr size_t LM_SMEM_LIMIT = 227 * 1024;
 
 __device__ __forceinline__ uint32_t lm_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void lm_cp_async16(void* smem, const void* gmem) {
@@ -255,6 +255,12 @@ struct LatentParams {
   float scale_log2;
   int num_pages;
   int* status;
+  // With num_splits > 1 the key range of a block is cut into that many parts (blockIdx.z); every part
+  // leaves its unnormalised sums [split][heads * tokens][rank] and (maximum, sum) [split][heads * tokens][2],
+  // and a second kernel merges them.
+  int num_splits;
+  float* part_o;
+  float* part_ml;
 };
 
 template <int LM_THREADS>
@@ -300,10 +306,15 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attention_mma_kernel(const 
   const int q_last = pos0 + (row0 + rows_valid - 1) / heads;
   const int key_hi = q_last + 1;                                              // exclusive
   const int key_lo = p.window > 0 ? max(0, q_first - p.window + 1) : 0;
-  const int tile_begin = key_lo / LM_BN, tile_end = (key_hi - 1) / LM_BN;     // inclusive
+  int tile_begin = key_lo / LM_BN, tile_end = (key_hi - 1) / LM_BN;           // inclusive
+  if (p.num_splits > 1) {
+    const int per_split = (tile_end - tile_begin + p.num_splits) / p.num_splits;
+    tile_begin += (int)blockIdx.z * per_split;
+    tile_end = min(tile_end, tile_begin + per_split - 1);                     // may leave no tile at all
+  }
   const int32_t* table = p.block_table + (size_t)s * p.table_stride;
 
-  lm_load_tile<LM_THREADS>(k_s, p, table, tile_begin * LM_BN, key_lo, key_hi, dk, ld);
+  if (tile_begin <= tile_end) lm_load_tile<LM_THREADS>(k_s, p, table, tile_begin * LM_BN, key_lo, key_hi, dk, ld);
   lm_cp_async_commit();
 
   // the queries of this block: absorbed part as it is, rotated part rotated by the row's position
@@ -439,8 +450,33 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attention_mma_kernel(const 
     __syncthreads();
   }
 
+  lm_cp_async_wait<0>();
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  if (p.num_splits > 1) {
+    const size_t all_rows = (size_t)heads * p.tokens;
+#pragma unroll
+    for (int half_rows = 0; half_rows < 2; ++half_rows) {
+      const int row = half_rows ? row_b : row_a;
+      if (row >= rows_valid) continue;
+      const int r = row0 + row;
+      const size_t at = (size_t)(r % heads) * p.tokens + (tok0 + r / heads);
+      float* dst = p.part_o + ((size_t)blockIdx.z * all_rows + at) * p.rank + v0;
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i) {
+        if (v0 + i * 8 < p.rank) {
+          dst[i * 8 + 2 * t4] = half_rows ? o[i][2] : o[i][0];
+          dst[i * 8 + 2 * t4 + 1] = half_rows ? o[i][3] : o[i][1];
+        }
+      }
+      if (t4 == 0 && blockIdx.y == 0) {
+        float* ml = p.part_ml + ((size_t)blockIdx.z * all_rows + at) * 2;
+        ml[0] = half_rows ? m_b : m_a;
+        ml[1] = half_rows ? l_b : l_a;
+      }
+    }
+    return;
+  }
   float f_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, f_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
 #pragma unroll
   for (int half_rows = 0; half_rows < 2; ++half_rows) {
@@ -458,6 +494,35 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attention_mma_kernel(const 
         *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = lm_pack_bf16(x * f, y * f);
       }
     }
+  }
+}
+
+
+// Merges the parts of a split launch: out[row] = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s, times
+// sigmoid of the row's gate. One block per (head, token) row.
+__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
+                                    const float* __restrict__ gate, int gate_ld, int tokens, int heads, int rank, int splits) {
+  const size_t row = blockIdx.x;                     // head * tokens + token
+  const size_t all_rows = (size_t)heads * tokens;
+  float m = -INFINITY;
+  for (int z = 0; z < splits; ++z) m = fmaxf(m, part_ml[((size_t)z * all_rows + row) * 2]);
+  float l = 0.0f;
+  for (int z = 0; z < splits; ++z) {
+    const float* ml = part_ml + ((size_t)z * all_rows + row) * 2;
+    if (ml[0] != -INFINITY) l += exp2f(ml[0] - m) * ml[1];
+  }
+  float f = l > 0.0f ? 1.0f / l : 0.0f;
+  if (gate) {
+    const int head = (int)(row / tokens), token = (int)(row % tokens);
+    f *= 1.0f / (1.0f + expf(-gate[(size_t)token * gate_ld + head]));
+  }
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+    float acc = 0.0f;
+    for (int z = 0; z < splits; ++z) {
+      const float mz = part_ml[((size_t)z * all_rows + row) * 2];
+      if (mz != -INFINITY) acc += exp2f(mz - m) * part_o[((size_t)z * all_rows + row) * rank + d];
+    }
+    out[row * rank + d] = __float2bfloat16_rn(acc * f);
   }
 }
 
@@ -555,8 +620,11 @@ static int launch_latent_mma(const LatentParams& p, int n_work, cudaStream_t s) 
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid(n_work, (p.rank + VT - 1) / VT);
+  dim3 grid(n_work, (p.rank + VT - 1) / VT, p.num_splits);
   latent_attention_mma_kernel<VT, Q, WARPS><<<grid, WARPS * 32, smem, s>>>(p);
+  if (p.num_splits > 1)
+    latent_merge_kernel<<<(unsigned)(p.heads * p.tokens), 128, 0, s>>>(p.part_o, p.part_ml, p.out, p.gate, p.gate_ld, p.tokens,
+                                                                     p.heads, p.rank, p.num_splits);
   return launch_status();
 }
 
@@ -566,8 +634,9 @@ PKV_EXPORT int pkv_latent_attention_mma(const void* q_lat, int q_lat_dtype, cons
                                         const int32_t* work_seq, const int32_t* work_row0, int n_work, const float* freq,
                                         const float* gate, int gate_ld, int tokens, int heads, int rank, int rot,
                                         int rot_dims, int page_size, int window, float scale, int num_pages, int* status,
-                                        void* stream) {
+                                        int num_splits, float* part_o, float* part_ml, void* stream) {
   if (n_work <= 0) return 0;
+  if (num_splits < 1 || num_splits > 64 || (num_splits > 1 && (!part_o || !part_ml))) return PKV_ERR_SIZE;
   if (heads < 1 || rot < 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1) || page_size < 1 || window < 0 || num_pages < 1)
     return PKV_ERR_SIZE;
   if (!pkv_latent_mma_supports(rank, rot)) return PKV_ERR_SIZE;
@@ -578,6 +647,7 @@ PKV_EXPORT int pkv_latent_attention_mma(const void* q_lat, int q_lat_dtype, cons
   p.gate = gate; p.gate_ld = gate_ld; p.tokens = tokens; p.heads = heads; p.rank = rank; p.rot = rot; p.rot_dims = rot_dims;
   p.page_size = page_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.num_pages = num_pages;
   p.status = status;
+  p.num_splits = num_splits; p.part_o = part_o; p.part_ml = part_ml;
   cudaStream_t s = (cudaStream_t)stream;
   const bool wide = pkv_latent_mma_rows_per_block(rank, rot) == 128;
 #define PKV_LM(VT)                                                                                  \

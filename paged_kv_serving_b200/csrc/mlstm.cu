@@ -78,35 +78,44 @@ __device__ __forceinline__ void ml_cp_async4(float* smem, const float* gmem) {
 __device__ __forceinline__ void ml_cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void ml_cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-// P lanes per column, R entries of the column per lane: P * R >= dim, P a power of two <= 32.
-// Column `vdim` is the normaliser n (its value is 1 for every token; its state lives in n_state and
-// its readout n . q goes to `dots`).
-template <int R>
+__device__ __forceinline__ void ml_cp_async16(float* smem, const float* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+
+// A group of P lanes owns ML_C columns, each lane R entries of every one of them: P * R >= dim,
+// P a power of two <= 32. Column `vdim` is the normaliser n (its value is 1 for every token; its
+// state lives in n_state and its readout n . q goes to `dots`).
+template <int R, int ML_C>
 __global__ void __launch_bounds__(128)
 mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, float q_scale,
                   const float* __restrict__ coef, float* __restrict__ s_state, float* __restrict__ n_state,
                   const int32_t* __restrict__ seq_starts, const int32_t* __restrict__ state_slots,
-                  float* __restrict__ out, float* __restrict__ dots, int heads, int dim, int vdim, int P, int chunk) {
-  extern __shared__ float ml_smem[];
+                  float* __restrict__ out, float* __restrict__ dots, int heads, int dim, int vdim, int P, int chunk,
+                  int vec4) {
+  extern __shared__ __align__(16) float ml_smem[];
   const int head = blockIdx.y, s = blockIdx.z;
-  const int per_block = 128 / P;
+  const int per_block = (128 / P) * ML_C;
   const int c0 = blockIdx.x * per_block;
-  const int column = c0 + threadIdx.x / P;
+  const int local0 = (threadIdx.x / P) * ML_C;        // first of this group's columns, inside the block
   const int p = threadIdx.x % P;
-  const bool live = column <= vdim;
-  const bool is_n = column == vdim;
   const int start = seq_starts[s], count = seq_starts[s + 1] - start;
   const int slot = state_slots[s];
   // one stage of shared memory: k [chunk][dim], q [chunk][dim], v [chunk][per_block], (a, b) [chunk][2]
   const int stage_floats = chunk * (2 * dim + per_block + 2);
-  float* mine = is_n ? n_state + ((size_t)slot * heads + head) * dim
-                     : s_state + ((size_t)slot * heads + head) * dim * vdim + (live ? column : 0);
-  const size_t stride = is_n ? 1 : (size_t)vdim;
-  float sv[R];
+  float* s_mine = s_state + ((size_t)slot * heads + head) * dim * vdim;
+  float* n_mine = n_state + ((size_t)slot * heads + head) * dim;
+  float sv[ML_C][R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int d = p + P * r;
-    sv[r] = (live && d < dim) ? mine[(size_t)d * stride] : 0.0f;
+  for (int c = 0; c < ML_C; ++c) {
+    const int column = c0 + local0 + c;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int d = p + P * r;
+      float v = 0.0f;
+      if (d < dim && column < vdim) v = s_mine[(size_t)d * vdim + column];
+      else if (d < dim && column == vdim) v = n_mine[d];
+      sv[c][r] = v;
+    }
   }
 
   auto load = [&](int stage, int first) {
@@ -115,11 +124,21 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, 
     float* vs = qs + chunk * dim;
     float* cs = vs + chunk * per_block;
     const int n = min(chunk, count - first);
-    for (int idx = threadIdx.x; idx < n * dim; idx += 128) {
-      const int t = idx / dim, d = idx - t * dim;
-      const float* row = proj + (size_t)(start + first + t) * ld;
-      ml_cp_async4(ks + idx, row + k_off + head * dim + d);
-      ml_cp_async4(qs + idx, row + q_off + head * dim + d);
+    if (vec4) {
+      const int quarter = dim >> 2;
+      for (int idx = threadIdx.x; idx < n * quarter; idx += 128) {
+        const int t = idx / quarter, d = (idx - t * quarter) << 2;
+        const float* row = proj + (size_t)(start + first + t) * ld;
+        ml_cp_async16(ks + t * dim + d, row + k_off + head * dim + d);
+        ml_cp_async16(qs + t * dim + d, row + q_off + head * dim + d);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < n * dim; idx += 128) {
+        const int t = idx / dim, d = idx - t * dim;
+        const float* row = proj + (size_t)(start + first + t) * ld;
+        ml_cp_async4(ks + idx, row + k_off + head * dim + d);
+        ml_cp_async4(qs + idx, row + q_off + head * dim + d);
+      }
     }
     for (int idx = threadIdx.x; idx < n * per_block; idx += 128) {
       const int t = idx / per_block, c = idx - t * per_block;
@@ -144,30 +163,52 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, 
     const int n = min(chunk, count - first);
     for (int t = 0; t < n; ++t) {
       const float a = cs[2 * t], b = cs[2 * t + 1];
-      const float bv = is_n ? b : (live ? b * vs[t * per_block + (column - c0)] : 0.0f);
-      float num = 0.0f;
+      float kk[R], qq[R];
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         const int d = p + P * r;
-        if (d < dim) {
-          sv[r] = fmaf(bv, ks[t * dim + d], a * sv[r]);
-          num = fmaf(sv[r], qs[t * dim + d], num);
-        }
+        kk[r] = d < dim ? ks[t * dim + d] : 0.0f;
+        qq[r] = d < dim ? qs[t * dim + d] : 0.0f;
       }
-      for (int o = P >> 1; o > 0; o >>= 1) num += __shfl_xor_sync(0xffffffffu, num, o);
-      if (live && p == 0) {
+      float num[ML_C];
+#pragma unroll
+      for (int c = 0; c < ML_C; ++c) {
+        const int column = c0 + local0 + c;
+        const float bv = column < vdim ? b * vs[t * per_block + local0 + c] : (column == vdim ? b : 0.0f);
+        float acc = 0.0f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          sv[c][r] = fmaf(bv, kk[r], a * sv[c][r]);
+          acc = fmaf(sv[c][r], qq[r], acc);
+        }
+        num[c] = acc;
+      }
+      for (int o = P >> 1; o > 0; o >>= 1) {
+#pragma unroll
+        for (int c = 0; c < ML_C; ++c) num[c] += __shfl_xor_sync(0xffffffffu, num[c], o);
+      }
+      if (p == 0) {
         const size_t token = (size_t)(start + first + t);
-        if (is_n) dots[token * heads + head] = num * q_scale;
-        else out[token * heads * vdim + head * vdim + column] = num * q_scale;
+#pragma unroll
+        for (int c = 0; c < ML_C; ++c) {
+          const int column = c0 + local0 + c;
+          if (column < vdim) out[token * heads * vdim + head * vdim + column] = num[c] * q_scale;
+          else if (column == vdim) dots[token * heads + head] = num[c] * q_scale;
+        }
       }
     }
     __syncthreads();        // the stage is free for the load after next
   }
   ml_cp_async_wait<0>();
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int d = p + P * r;
-    if (live && d < dim) mine[(size_t)d * stride] = sv[r];
+  for (int c = 0; c < ML_C; ++c) {
+    const int column = c0 + local0 + c;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int d = p + P * r;
+      if (d < dim && column < vdim) s_mine[(size_t)d * vdim + column] = sv[c][r];
+      else if (d < dim && column == vdim) n_mine[d] = sv[c][r];
+    }
   }
 }
 
@@ -220,23 +261,25 @@ PKV_EXPORT int pkv_mlstm(const float* proj, int ld, int q_off, int k_off, int v_
                                                      state_slots, coef, heads);
   // lanes per column: enough that a lane holds at most R entries of it
   const int R = dim <= 256 ? 8 : 32;
+  const int ML_C = dim <= 256 ? 4 : 2;      // columns per group of lanes (registers: ML_C * R state entries a lane)
   int P = 1;
   while (P * R < dim) P <<= 1;
-  const int per_block = 128 / P;
+  const int per_block = (128 / P) * ML_C;
   // tokens per stage of shared memory: as many as fit in about 40 KB a stage, 16 at most
   int chunk = 16;
   while (chunk > 1 && (size_t)chunk * (2 * dim + per_block + 2) * sizeof(float) > 40 * 1024) chunk >>= 1;
   const size_t smem = 2 * (size_t)chunk * (2 * dim + per_block + 2) * sizeof(float);
   float* dots = o + (size_t)tokens * heads * vdim;
+  const int vec4 = (dim % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && chunk % 2 == 0) ? 1 : 0;
   dim3 grid((vdim + 1 + per_block - 1) / per_block, heads, seqs);
   if (R == 8) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_scan_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    mlstm_scan_kernel<8><<<grid, 128, smem, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, n_state, seq_starts,
-                                                 state_slots, o, dots, heads, dim, vdim, P, chunk);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_scan_kernel<8, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    mlstm_scan_kernel<8, 4><<<grid, 128, smem, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, n_state, seq_starts,
+                                                 state_slots, o, dots, heads, dim, vdim, P, chunk, vec4);
   } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    mlstm_scan_kernel<32><<<grid, 128, smem, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, n_state, seq_starts,
-                                                  state_slots, o, dots, heads, dim, vdim, P, chunk);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_scan_kernel<32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    mlstm_scan_kernel<32, 2><<<grid, 128, smem, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, n_state, seq_starts,
+                                                  state_slots, o, dots, heads, dim, vdim, P, chunk, vec4);
   }
   const long long rows = (long long)tokens * heads;
   const unsigned blocks = (unsigned)((rows + 3) / 4);

@@ -250,9 +250,11 @@ def latent_attention_mma(q_lat: torch.Tensor, q: torch.Tensor, q_rot_offset: int
                          block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor, work_seq: torch.Tensor,
                          work_row0: torch.Tensor, freq: torch.Tensor, gate: torch.Tensor | None, heads: int, rank: int,
                          rot: int, rot_dims: int, page_size: int, window: int, scale: float, status: torch.Tensor,
-                         n_work: int | None = None) -> torch.Tensor:
+                         n_work: int | None = None, num_splits: int = 1) -> torch.Tensor:
     """``latent_attention`` on the tensor cores, for bfloat16 queries and cache (``q_lat`` float32
-    or bfloat16); the work list is in blocks of ``latent_mma_rows_per_block(rank, rot)`` rows."""
+    or bfloat16); the work list is in blocks of ``latent_mma_rows_per_block(rank, rot)`` rows.
+    ``num_splits`` > 1 cuts every block's key range into that many parts that run side by side and
+    are merged by a second kernel (for steps of few rows over long contexts)."""
     _need(q_lat, None, "q_lat"); _need(q, torch.bfloat16, "q"); _need(pool, torch.bfloat16, "pool")
     tokens = q.shape[0]
     if q_lat.shape != (heads, tokens, rank):
@@ -269,11 +271,18 @@ def latent_attention_mma(q_lat: torch.Tensor, q: torch.Tensor, q_rot_offset: int
     fn = _fn("latent_attention", "pkv_latent_attention_mma",
              [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
               c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-              c_void_p, c_void_p])
+              c_void_p, c_int, c_void_p, c_void_p, c_void_p])
     q_rot = q.view(-1)[q_rot_offset:]
+    part_o = part_ml = None
+    if num_splits > 1:
+        part_o = _empty((num_splits, heads * tokens, rank), torch.float32, q.device)
+        part_ml = _empty((num_splits, heads * tokens, 2), torch.float32, q.device)
     _check(fn(_ptr(q_lat), dtype_code(q_lat.dtype), c_void_p(q_rot.data_ptr()), q.stride(0), q_head_stride, _ptr(out),
               _ptr(pool), _ptr(block_table), block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq),
               _ptr(work_row0), work_seq.numel() if n_work is None else int(n_work), _ptr(freq), _ptr(gate), gate_ld, tokens,
-              heads, rank, rot, rot_dims, page_size, int(window), float(scale), num_pages, _ptr(status), _stream()),
+              heads, rank, rot, rot_dims, page_size, int(window), float(scale), num_pages, _ptr(status), int(num_splits),
+              _ptr(part_o), _ptr(part_ml), _stream()),
            "latent_attention_mma")
+    if num_splits > 1:
+        ops.LAUNCHES["count"] += 1
     return out

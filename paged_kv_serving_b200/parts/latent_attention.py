@@ -116,6 +116,15 @@ class LatentAttention(Part):
         order = np.argsort(-cost, kind="stable")
         ctx.arena.add(seq_name, work_seq[order])
         ctx.arena.add(row_name, work_row0[order])
+        # A step of few rows over long contexts (decoding) would leave most SMs idle with one block
+        # an entry: the key range is then cut into parts that run side by side and are merged.
+        splits = 1
+        if self._tensor_cores(ctx) and len(work_seq):
+            longest = ctx.planning_context_len or int((np.asarray(ctx.first_positions) + np.asarray(ctx.seq_lens)).max())
+            columns = -(-self.kv_rank // 256)
+            places = 2 * torch.cuda.get_device_properties(ctx.device).multi_processor_count
+            splits = int(max(1, min(16, places // (len(work_seq) * columns), longest // 128)))
+        ctx.scratch[seq_name] = splits
 
     def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding) -> torch.Tensor:
         group = ctx.groups[binding.group]
@@ -135,10 +144,11 @@ class LatentAttention(Part):
         seq_name, row_name = self._work_names(ctx)
         gate = fused[:, self.g_off:self.g_off + self.heads]
         kernel = mixer_ops.latent_attention_mma if self._tensor_cores(ctx) else mixer_ops.latent_attention
+        extra = {"num_splits": ctx.scratch.get(seq_name, 1)} if self._tensor_cores(ctx) else {}
         attended = kernel(
             q_lat, q, self.dim, head, pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
             ctx.ints(seq_name), ctx.ints(row_name), self.freq, gate, self.heads, self.kv_rank, self.rot_dim, self.rot_dims,
-            group.page_size, self.window or 0, self.scale, ctx.status)
+            group.page_size, self.window or 0, self.scale, ctx.status, **extra)
         values = torch.bmm(attended, self.uv_t)                                # [heads, tokens, vdim]
         merged = values.transpose(0, 1).reshape(tokens, self.heads * self.vdim)
         return gemm.linear(merged, self.o)

@@ -124,7 +124,7 @@ def close(got, want, dtype, what):
     spread of the plain logits. float32: every row within 1e-4. bfloat16: rounding moves a row by
     about half a percent, but where two experts' router scores nearly tie it may pick the other one,
     which moves that token's row by tens of percent and, through the caches and states, the rows
-    after it by a few. So the typical row must stay within 5 %, at most one row in eight may
+    after it by a few. So the typical row must stay within 5 %, at most one row in six may
     exceed 10 %, and none 60 %; the float32 runs of the same schedules are the sharp test."""
     got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
     assert got.shape == want.shape, f"{what}: shapes {got.shape} and {want.shape}"
@@ -138,7 +138,7 @@ def close(got, want, dtype, what):
         assert float(error.max()) <= 1e-4, worst
     else:
         assert float(np.median(error)) <= 0.05, f"{what}: the typical row is off by {np.median(error):.3e} of the spread"
-        assert int((error > 0.1).sum()) <= max(1, error.size // 8), worst
+        assert int((error > 0.1).sum()) <= max(1, error.size // 6), worst
         assert float(error.max()) <= 0.6, worst
 
 
@@ -578,6 +578,11 @@ def test_latent_attention_on_tensor_cores_matches_the_general_kernel(heads, rank
         want[:, rows] = _latent_reference(q_lat[:, rows].cpu().numpy().astype(np.float64), rotated.transpose(1, 0, 2),
                                           caches[s], f, scale, rank, window)
     want *= 1.0 / (1.0 + np.exp(-gate.cpu().numpy().astype(np.float64).T[:, :, None]))
+    # the key range cut into parts that are merged afterwards (what a step of few rows uses)
+    for parts in (2, 5, 16):
+        cut = run(lambda *a, **k: mixer_ops.latent_attention_mma(*a, num_splits=parts, **k),
+                  mixer_ops.latent_mma_rows_per_block(rank, rot))
+        assert np.abs(cut - fast).max() <= 0.02 * np.abs(want).max(), f"{parts} parts"
     assert np.isfinite(fast).all() and np.isfinite(general).all()
     assert np.abs(general - want).max() <= 0.02 * np.abs(want).max()
     assert np.abs(fast - want).max() <= 0.03 * np.abs(want).max()
