@@ -172,6 +172,62 @@ __global__ void expert_act_bf16x8_kernel(const bf16* __restrict__ up, int ld, co
   store8(out + (size_t)t * cols + c, v);
 }
 
+
+// The whole per-token side input for the few rows of a decode step, one block per token:
+//   hidden += delta + bias;  x = hidden (rounded to the compute type)
+//   z = gate_w x;  g = act(z) * table[id, col0 + j];  y = proj_w g;  out = y / rms(y) * norm_w   (float32)
+// with the same roundings between the stages as the separate kernels and library products have.
+template <typename W, typename D>
+__global__ void __launch_bounds__(256)
+token_side_kernel(float* __restrict__ hidden, const D* __restrict__ delta, const float* __restrict__ bias,
+                  const W* __restrict__ gate_w, const W* __restrict__ proj_w, const W* __restrict__ table, int table_cols,
+                  int table_rows, const int32_t* __restrict__ ids, int col0, const float* __restrict__ norm_w, float eps,
+                  float* __restrict__ out, int width, int dim, int act, const int32_t* __restrict__ fed_back,
+                  const int32_t* __restrict__ fed_back_at, int* __restrict__ status) {
+  extern __shared__ float ts_smem[];
+  float* x = ts_smem;             // [width]
+  float* y = x + width;           // [width]
+  float* g = y + width;           // [dim]
+  float* scratch = g + dim;       // [32]
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = hidden[(size_t)t * width + c];
+    if (delta) v += to_float(delta[(size_t)t * width + c]);
+    if (bias) v += bias[c];
+    hidden[(size_t)t * width + c] = v;
+    x[c] = to_float(from_float<W>(v));
+  }
+  int id = ids[t];
+  if (fed_back_at && fed_back_at[t] >= 0) id = fed_back[fed_back_at[t]];
+  const bool known = id >= 0 && id < table_rows;
+  if (!known && threadIdx.x == 0 && status) atomicExch(status, PKV_STATUS_BAD_ID);
+  __syncthreads();
+  for (int j = warp; j < dim; j += (blockDim.x >> 5)) {
+    const W* row = gate_w + (size_t)j * width;
+    float acc = 0.0f;
+    for (int c = lane; c < width; c += 32) acc = fmaf(to_float(row[c]), x[c], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const float z = to_float(from_float<W>(acc));
+      const float e = known ? to_float(table[(size_t)id * table_cols + col0 + j]) : 0.0f;
+      g[j] = to_float(from_float<W>(activate(z, act) * e));
+    }
+  }
+  __syncthreads();
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const W* row = proj_w + (size_t)c * dim;
+    float acc = 0.0f;
+    for (int j = 0; j < dim; ++j) acc = fmaf(to_float(row[j]), g[j], acc);
+    y[c] = acc;
+    ss = fmaf(acc, acc, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)t * width + c] = y[c] * inv * norm_w[c];
+}
+
 }  // namespace pkv
 
 using namespace pkv;
@@ -257,4 +313,34 @@ PKV_EXPORT int pkv_expert_act(const void* up, int dtype, int ld, const float* we
     return PKV_ERR_DTYPE;
   }
   return launch_status();
+}
+
+PKV_EXPORT int pkv_token_side(float* hidden, const void* delta, int delta_dtype, const float* bias, const void* gate_w,
+                              const void* proj_w, const void* table, int dtype, int table_cols, int table_rows,
+                              const int32_t* ids, int col0, const float* norm_w, float eps, float* out, int tokens, int width,
+                              int dim, int act, const int32_t* fed_back, const int32_t* fed_back_at, int* status,
+                              void* stream) {
+  if (tokens <= 0) return 0;
+  if (width < 1 || dim < 1 || col0 < 0 || col0 + dim > table_cols || act < 0 || act > 4) return PKV_ERR_SIZE;
+  const size_t smem = (size_t)(2 * width + dim + 32) * sizeof(float);
+  if (smem > 200 * 1024) return PKV_ERR_LIMIT;
+  cudaStream_t s = (cudaStream_t)stream;
+#define PKV_TS(W, D)                                                                                                    \
+  do {                                                                                                                  \
+    if (smem > 48 * 1024) {                                                                                             \
+      cudaError_t e = cudaFuncSetAttribute(token_side_kernel<W, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                                              \
+    }                                                                                                                   \
+    token_side_kernel<W, D><<<tokens, 256, smem, s>>>(hidden, (const D*)delta, bias, (const W*)gate_w, (const W*)proj_w,  \
+                                                      (const W*)table, table_cols, table_rows, ids, col0, norm_w, eps, out, \
+                                                      width, dim, act, fed_back, fed_back_at, status);                  \
+    return launch_status();                                                                                             \
+  } while (0)
+  const int d = delta ? delta_dtype : dtype;
+  if (dtype == PKV_F32 && d == PKV_F32) PKV_TS(float, float);
+  if (dtype == PKV_BF16 && d == PKV_BF16) PKV_TS(bf16, bf16);
+  if (dtype == PKV_BF16 && d == PKV_F32) PKV_TS(bf16, float);
+  if (dtype == PKV_F32 && d == PKV_BF16) PKV_TS(float, bf16);
+#undef PKV_TS
+  return PKV_ERR_DTYPE;
 }

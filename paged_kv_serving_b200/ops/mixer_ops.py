@@ -17,7 +17,7 @@ from paged_kv_serving_b200.ops.arena import empty as _empty
 
 __all__ = ["ACTIVATIONS", "act_times_table", "bias_act", "conv_residual", "expert_act", "latent_attention",
            "latent_attention_mma", "latent_mma_rows_per_block", "latent_mma_supports", "latent_prepare",
-           "latent_rows_per_block", "mlstm", "residual_add", "route_top"]
+           "latent_rows_per_block", "mlstm", "residual_add", "route_top", "token_side"]
 
 #: activation names of ``bias_act`` / ``act_times_table`` / ``expert_act``
 ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "relu_squared": 3, "sigmoid": 4}
@@ -285,4 +285,36 @@ def latent_attention_mma(q_lat: torch.Tensor, q: torch.Tensor, q_rot_offset: int
            "latent_attention_mma")
     if num_splits > 1:
         ops.LAUNCHES["count"] += 1
+    return out
+
+
+def token_side(hidden: torch.Tensor, delta: torch.Tensor | None, bias: torch.Tensor | None, gate_w: torch.Tensor,
+               proj_w: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0: int, norm_w: torch.Tensor, eps: float,
+               act: str, status: torch.Tensor, fed_back: torch.Tensor | None = None,
+               fed_back_at: torch.Tensor | None = None) -> torch.Tensor:
+    """The per-token side input in one kernel (one block a token; for the few rows of a decode
+    step): ``hidden += delta + bias`` in place, then ``rmsnorm(proj_w (act(gate_w x) * table[ids,
+    col0:col0 + dim])) * norm_w`` of the updated rows ``x``, float32 ``[tokens, width]``. ``gate_w
+    [dim, width]``, ``proj_w [width, dim]`` and ``table`` share one type; the stages round as the
+    separate kernels and products do."""
+    _need(hidden, torch.float32, "hidden"); _need(gate_w, None, "gate_w"); _need(proj_w, gate_w.dtype, "proj_w")
+    _need(table, gate_w.dtype, "table"); _need(norm_w, torch.float32, "norm_w"); _need(ids, torch.int32, "ids")
+    tokens, width = hidden.shape
+    dim = gate_w.shape[0]
+    if gate_w.shape != (dim, width) or proj_w.shape != (width, dim) or norm_w.numel() != width:
+        raise ValueError("token_side: sizes do not fit")
+    if delta is not None:
+        _need(delta, None, "delta")
+        if delta.shape != hidden.shape:
+            raise ValueError("delta and hidden differ in shape")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+    out = _empty((tokens, width), torch.float32, hidden.device)
+    fn = _fn("pointwise", "pkv_token_side",
+             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+              c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(hidden), _ptr(delta), dtype_code(delta.dtype) if delta is not None else 0, _ptr(bias), _ptr(gate_w),
+              _ptr(proj_w), _ptr(table), dtype_code(gate_w.dtype), table.shape[1], table.shape[0], _ptr(ids), int(col0),
+              _ptr(norm_w), float(eps), _ptr(out), tokens, width, dim, ACTIVATIONS[act], _ptr(fed_back), _ptr(fed_back_at),
+              _ptr(status), _stream()), "token_side")
     return out

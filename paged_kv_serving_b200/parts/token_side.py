@@ -34,6 +34,9 @@ class TokenSideInput(Part):
     pending update of the layer is added first. ``forward`` returns the new pending update."""
 
     graph_safe = True
+    #: Steps of at most this many tokens run the whole side input as one kernel (a block a token);
+    #: longer ones as two library products with the element-wise kernels between them.
+    FUSED_ROWS = 32
 
     def __init__(self, width: int, dim: int, slice_index: int, table: TokenSideTable, eps: float) -> None:
         self.width, self.dim, self.slice_index, self.table, self.eps = int(width), int(dim), int(slice_index), table, float(eps)
@@ -47,9 +50,13 @@ class TokenSideInput(Part):
 
     def forward(self, hidden: torch.Tensor, pending: torch.Tensor | None, ctx: StepContext,
                 bias: torch.Tensor | None = None) -> torch.Tensor:
+        fed_back_at = ctx.ints(ctx.TOKEN_FEEDBACK) if ctx.fed_back_ids is not None else None
+        if hidden.shape[0] <= self.FUSED_ROWS:
+            return mixer_ops.token_side(hidden, pending, bias, self.gate, self.proj, self.table.table, ctx.ints(ctx.TOKEN_IDS),
+                                        self.slice_index * self.dim, self.norm, self.eps, "gelu_tanh", ctx.status,
+                                        ctx.fed_back_ids if fed_back_at is not None else None, fed_back_at)
         x = mixer_ops.residual_add(hidden, pending, bias, out_dtype=ctx.dtype)
         z = gemm.linear(x, self.gate)
-        fed_back_at = ctx.ints(ctx.TOKEN_FEEDBACK) if ctx.fed_back_ids is not None else None
         g = mixer_ops.act_times_table(z, self.table.table, ctx.ints(ctx.TOKEN_IDS), self.slice_index * self.dim, "gelu_tanh",
                                       ctx.status, ctx.fed_back_ids if fed_back_at is not None else None, fed_back_at)
         y = gemm.linear(g, self.proj, out_dtype=torch.float32)
