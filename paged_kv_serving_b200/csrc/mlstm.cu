@@ -261,7 +261,9 @@ PKV_EXPORT int pkv_mlstm(const float* proj, int ld, int q_off, int k_off, int v_
                                                      state_slots, coef, heads);
   // lanes per column: enough that a lane holds at most R entries of it
   const int R = dim <= 256 ? 8 : 32;
-  const int ML_C = dim <= 256 ? 4 : 2;      // columns per group of lanes (registers: ML_C * R state entries a lane)
+  // columns per group of lanes (registers: ML_C * R state entries a lane). Two columns a group, which doubles
+  // the blocks of a single long prompt, measured slower than four (keys and queries are staged twice as often).
+  const int ML_C = dim <= 256 ? 4 : 2;
   int P = 1;
   while (P * R < dim) P <<= 1;
   const int per_block = (128 / P) * ML_C;

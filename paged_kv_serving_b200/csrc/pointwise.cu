@@ -173,6 +173,27 @@ __global__ void expert_act_bf16x8_kernel(const bf16* __restrict__ up, int ld, co
 }
 
 
+// Dot product of `n` weights with float values in shared memory; 16-byte loads for bfloat16 rows
+// that start on 16-byte boundaries (n a multiple of 8), lane-strided otherwise.
+__device__ __forceinline__ float row_dot_strided(const float* w, const float* v, int n, int first, int step) {
+  float acc = 0.0f;
+  for (int c = first; c < n; c += step) acc = fmaf(w[c], v[c], acc);
+  return acc;
+}
+__device__ __forceinline__ float row_dot_strided(const bf16* w, const float* v, int n, int first, int step) {
+  float acc = 0.0f;
+  if ((n & 7) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (int c = first * 8; c < n; c += step * 8) {
+      const Pack8 x = load8(w + c);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc = fmaf(x.v[k], v[c + k], acc);
+    }
+    return acc;
+  }
+  for (int c = first; c < n; c += step) acc = fmaf(to_float(w[c]), v[c], acc);
+  return acc;
+}
+
 // The whole per-token side input for the few rows of a decode step, one block per token:
 //   hidden += delta + bias;  x = hidden (rounded to the compute type)
 //   z = gate_w x;  g = act(z) * table[id, col0 + j];  y = proj_w g;  out = y / rms(y) * norm_w   (float32)
@@ -204,9 +225,7 @@ token_side_kernel(float* __restrict__ hidden, const D* __restrict__ delta, const
   if (!known && threadIdx.x == 0 && status) atomicExch(status, PKV_STATUS_BAD_ID);
   __syncthreads();
   for (int j = warp; j < dim; j += (blockDim.x >> 5)) {
-    const W* row = gate_w + (size_t)j * width;
-    float acc = 0.0f;
-    for (int c = lane; c < width; c += 32) acc = fmaf(to_float(row[c]), x[c], acc);
+    float acc = row_dot_strided(gate_w + (size_t)j * width, x, width, lane, 32);
     acc = warp_sum(acc);
     if (lane == 0) {
       const float z = to_float(from_float<W>(acc));
@@ -217,9 +236,7 @@ token_side_kernel(float* __restrict__ hidden, const D* __restrict__ delta, const
   __syncthreads();
   float ss = 0.0f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    const W* row = proj_w + (size_t)c * dim;
-    float acc = 0.0f;
-    for (int j = 0; j < dim; ++j) acc = fmaf(to_float(row[j]), g[j], acc);
+    const float acc = row_dot_strided(proj_w + (size_t)c * dim, g, dim, 0, 1);
     y[c] = acc;
     ss = fmaf(acc, acc, ss);
   }

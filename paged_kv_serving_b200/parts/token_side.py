@@ -34,9 +34,12 @@ class TokenSideInput(Part):
     pending update of the layer is added first. ``forward`` returns the new pending update."""
 
     graph_safe = True
-    #: Steps of at most this many tokens run the whole side input as one kernel (a block a token);
-    #: longer ones as two library products with the element-wise kernels between them.
-    FUSED_ROWS = 32
+    #: Steps of at most this many tokens run the whole side input as one kernel (a block a token)
+    #: instead of two library products with the element-wise kernels between them. Off (0): measured
+    #: inside captured decode steps of 8 requests the one kernel is slower than the five launches it
+    #: replaces (0.68 against 0.60 ms a step at width 2,048, 1.37 against 1.20 at 4,096): a block a
+    #: token leaves the two matrices to eight SMs. Tests run it.
+    FUSED_ROWS = 0
 
     def __init__(self, width: int, dim: int, slice_index: int, table: TokenSideTable, eps: float) -> None:
         self.width, self.dim, self.slice_index, self.table, self.eps = int(width), int(dim), int(slice_index), table, float(eps)

@@ -586,3 +586,24 @@ def test_latent_attention_on_tensor_cores_matches_the_general_kernel(heads, rank
     assert np.isfinite(fast).all() and np.isfinite(general).all()
     assert np.abs(general - want).max() <= 0.02 * np.abs(want).max()
     assert np.abs(fast - want).max() <= 0.03 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_side_input_as_one_kernel_equals_the_separate_kernels(dtype):
+    """The switch that sends steps of few rows through the one-kernel form of the side input."""
+    from paged_kv_serving_b200.parts.token_side import TokenSideInput
+
+    config = CONFIGS["C"]
+    tensors = random_tensors(config, seed=51)
+    tokens = tokens_for(config, 40, seed=8)
+    want = plain_logits(config, tensors, tokens)
+    before = TokenSideInput.FUSED_ROWS
+    TokenSideInput.FUSED_ROWS = 16
+    try:
+        session = session_for(config, tensors, dtype, page=PAGE["C"])
+        rows = [session.step([{"id": "r", "tokens": tokens[:20], "want": list(range(20))}]),        # separate kernels
+                session.step([{"id": "r", "tokens": tokens[20:33], "want": list(range(13))}])]       # one kernel
+        rows += [session.step([{"id": "r", "tokens": [t], "want": [0]}]) for t in tokens[33:]]
+    finally:
+        TokenSideInput.FUSED_ROWS = before
+    close(np.concatenate(rows), want, dtype, "side input, one kernel")
