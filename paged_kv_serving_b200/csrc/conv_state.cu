@@ -36,6 +36,62 @@ __global__ void conv_residual_kernel(const X* __restrict__ x, const float* __res
   out[i] = from_float<X>(own + acc);
 }
 
+// The same for bfloat16 rows whose width is a multiple of 8: a thread takes 8 channels of a token
+// with 16-byte loads and stores; the weights arrive transposed, w_t [taps][width], so that the 8
+// channels' weights of a tap are two 16-byte loads as well.
+__global__ void conv_residual_bf16x8_kernel(const bf16* __restrict__ x, const float* __restrict__ w_t,
+                                            const bf16* __restrict__ state, const int32_t* __restrict__ token_seq,
+                                            const int32_t* __restrict__ seq_starts, const int32_t* __restrict__ state_slots,
+                                            bf16* __restrict__ out, int tokens, int width, int taps) {
+  const int per_row = width >> 3;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= tokens * per_row) return;
+  const int t = i / per_row, c = (i - t * per_row) << 3;
+  const int s = token_seq[t];
+  const int local = t - seq_starts[s];
+  const int slot = state_slots[s];
+  const int tail = taps - 1;
+  float own[8], acc[8];
+  {
+    const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)t * width + c);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      own[2 * k] = f.x;
+      own[2 * k + 1] = f.y;
+    }
+  }
+  {
+    const float4 lo = *reinterpret_cast<const float4*>(w_t + (size_t)tail * width + c);
+    const float4 hi = *reinterpret_cast<const float4*>(w_t + (size_t)tail * width + c + 4);
+    const float wk[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = own[k] * wk[k];
+  }
+  for (int j = 0; j < tail; ++j) {
+    const int src = local - tail + j;
+    const bf16* from = src >= 0 ? x + (size_t)(t - tail + j) * width + c
+                                : state + ((size_t)slot * tail + (tail + src)) * width + c;
+    const uint4 raw = *reinterpret_cast<const uint4*>(from);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float4 lo = *reinterpret_cast<const float4*>(w_t + (size_t)j * width + c);
+    const float4 hi = *reinterpret_cast<const float4*>(w_t + (size_t)j * width + c + 4);
+    const float wk[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      acc[2 * k] = fmaf(wk[2 * k], f.x, acc[2 * k]);
+      acc[2 * k + 1] = fmaf(wk[2 * k + 1], f.y, acc[2 * k + 1]);
+    }
+  }
+  uint4 packed;
+  __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(own[2 * k] + acc[2 * k], own[2 * k + 1] + acc[2 * k + 1]);
+  *reinterpret_cast<uint4*>(out + (size_t)t * width + c) = packed;
+}
+
 template <typename X>
 __global__ void conv_state_update_kernel(const X* __restrict__ x, X* __restrict__ state,
                                          const int32_t* __restrict__ seq_starts, const int32_t* __restrict__ state_slots,
@@ -58,7 +114,8 @@ __global__ void conv_state_update_kernel(const X* __restrict__ x, X* __restrict_
 
 using namespace pkv;
 
-PKV_EXPORT int pkv_conv_residual(const void* x, int dtype, const float* w, void* state, const int32_t* token_seq,
+// w: [width][taps]; w_t: the same weights as [taps][width], or null (the 16-byte form needs it).
+PKV_EXPORT int pkv_conv_residual(const void* x, int dtype, const float* w, const float* w_t, void* state, const int32_t* token_seq,
                                  const int32_t* seq_starts, const int32_t* state_slots, void* out, int tokens, int seqs,
                                  int width, int taps, void* stream) {
   if (tokens <= 0) return 0;
@@ -74,7 +131,13 @@ PKV_EXPORT int pkv_conv_residual(const void* x, int dtype, const float* w, void*
       conv_state_update_kernel<float><<<state_blocks, 256, 0, s>>>((const float*)x, (float*)state, seq_starts, state_slots,
                                                                    seqs, width, taps);
   } else if (dtype == PKV_BF16) {
-    conv_residual_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)x, w, (const bf16*)state, token_seq, seq_starts,
+    const bool wide = w_t != nullptr && ((uintptr_t)w_t & 15) == 0 && width % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                      (taps == 1 || ((uintptr_t)state & 15) == 0) && total / 8 < (1ll << 31);
+    if (wide)
+      conv_residual_bf16x8_kernel<<<(unsigned)((total / 8 + 255) / 256), 256, 0, s>>>(
+          (const bf16*)x, w_t, (const bf16*)state, token_seq, seq_starts, state_slots, (bf16*)out, tokens, width, taps);
+    else
+      conv_residual_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)x, w, (const bf16*)state, token_seq, seq_starts,
                                                       state_slots, (bf16*)out, tokens, width, taps);
     if (taps > 1)
       conv_state_update_kernel<bf16><<<state_blocks, 256, 0, s>>>((const bf16*)x, (bf16*)state, seq_starts, state_slots,

@@ -109,11 +109,16 @@ def expert_act(up: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor | Non
 
 
 def conv_residual(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, token_seq: torch.Tensor,
-                  seq_starts: torch.Tensor, state_slots: torch.Tensor) -> torch.Tensor:
+                  seq_starts: torch.Tensor, state_slots: torch.Tensor, weight_t: torch.Tensor | None = None) -> torch.Tensor:
     """``x + causal_conv(x)`` per channel for a ragged batch, ``weight [width, taps]`` float32 with
     tap ``taps - 1`` on the token itself; ``state [slots, taps - 1, width]`` (type of ``x``) holds
-    every request's last inputs and is brought up to date."""
+    every request's last inputs and is brought up to date. ``weight_t`` (the weights as ``[taps,
+    width]``) lets bfloat16 rows of a width that is a multiple of 8 take the 16-byte kernel."""
     _need(x, None, "x"); _need(weight, torch.float32, "weight")
+    if weight_t is not None:
+        _need(weight_t, torch.float32, "weight_t")
+        if weight_t.shape != (weight.shape[1], weight.shape[0]):
+            raise ValueError("weight_t must be the transpose of weight")
     tokens, width = x.shape
     taps = weight.shape[1]
     if weight.shape[0] != width:
@@ -125,8 +130,9 @@ def conv_residual(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | N
     seqs = seq_starts.numel() - 1
     out = _empty((tokens, width), x.dtype, x.device)
     fn = _fn("conv_state", "pkv_conv_residual",
-             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check(fn(_ptr(x), dtype_code(x.dtype), _ptr(weight), _ptr(state), _ptr(token_seq), _ptr(seq_starts), _ptr(state_slots),
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+              c_void_p])
+    _check(fn(_ptr(x), dtype_code(x.dtype), _ptr(weight), _ptr(weight_t), _ptr(state), _ptr(token_seq), _ptr(seq_starts), _ptr(state_slots),
               _ptr(out), tokens, seqs, width, taps, _stream()), "conv_residual")
     ops.LAUNCHES["count"] += 1 if taps > 1 else 0
     return out

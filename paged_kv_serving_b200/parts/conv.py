@@ -30,6 +30,10 @@ class ResidualCausalConv(Part):
     def param_specs(self) -> dict[str, ParamSpec]:
         return {"weight": ParamSpec((self.width, self.taps), "vector")}
 
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        self.weight = params["weight"].contiguous()
+        self.weight_t = self.weight.t().contiguous()          # [taps, width], what the 16-byte kernel reads
+
     def state_requests(self) -> dict[str, StateRequest]:
         if self.taps == 1:
             return {}
@@ -38,4 +42,4 @@ class ResidualCausalConv(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding) -> torch.Tensor:
         state = ctx.states[binding.extra[self.STATE]] if self.taps > 1 else None
         return mixer_ops.conv_residual(x, self.weight, state, ctx.ints(ctx.TOKEN_SEQ), ctx.ints(ctx.SEQ_STARTS),
-                                       ctx.ints(ctx.STATE_SLOTS))
+                                       ctx.ints(ctx.STATE_SLOTS), self.weight_t)
