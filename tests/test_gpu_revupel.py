@@ -314,18 +314,20 @@ def _single(mixer, mlp=None, **extra):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("what", ("attention", "attention_partly_rotated", "mlstm", "mlstm_wide_keys", "dense", "routed_top_all",
-                                  "routed_no_shared", "conv", "side"))
+@pytest.mark.parametrize("what", ("attention", "attention_partly_rotated", "mlstm", "mlstm_wide_keys", "mlstm_very_wide_keys",
+                                  "dense", "routed_top_all", "routed_no_shared", "conv", "conv_one_tap", "side"))
 def test_each_mechanism_alone(what, dtype):
     config = {
         "attention": _single(_attention(2, 8, 8, 16, 8, 24)),
         "attention_partly_rotated": _single(_attention(4, 4, 12, 4, 12, 8, rot_dims=6)),
         "mlstm": _single(_mlstm(2, 8, 12, 6.0)),
         "mlstm_wide_keys": _single(_mlstm(1, 72, 8, 20.0)),
+        "mlstm_very_wide_keys": _single(_mlstm(2, 288, 6, 20.0)),          # the kernels' form for keys beyond 256
         "dense": _single(_attention(1, 8, 4, 8, 8, 8), _dense(20)),
         "routed_top_all": _single(_attention(1, 8, 4, 8, 8, 8), _moe(3, 3, 8, 8)),
         "routed_no_shared": _single(_attention(1, 8, 4, 8, 8, 8), _moe(7, 2, 8, 0)),
         "conv": _single(_mlstm(2, 8, 8, 9.0), canon={"taps": 5}),
+        "conv_one_tap": _single(_mlstm(2, 8, 8, 9.0), canon={"taps": 1}),     # no tail, no state
         "side": _single(_mlstm(2, 8, 8, 9.0), token_side={"dim": 7}),
     }[what]
     tensors = random_tensors(config, seed=31, scale=2.0)
