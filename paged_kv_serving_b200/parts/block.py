@@ -138,10 +138,21 @@ class ConvSideBlock(Block):
         h = self.mixer_norm.add_norm(hidden, pending, ctx.dtype)
         if self.input_conv is not None:
             h = self.input_conv.forward(h, ctx, binding)
-        update = self.mixer.forward(h, ctx, binding)
         bias = None
+        follow = getattr(self.ff_norm, "add_norm_of_linear", None) if self.feed_forward is not None else None
+        if follow is not None and self.mixer.fuses_last_linear:
+            # the mixer's last product carries the residual add, and for the few rows of a decode step
+            # leaves the norm to the product that reads it
+            chain = self.mixer.chains_last_linear
+            h = self.mixer.forward(h, ctx, binding, finish=lambda x, w: follow(hidden, x, w, ctx.dtype, chain=chain))
+            if not self.feed_forward.accepts_pending_norm:
+                h = gemm.as_tensor(h)
+            update = None
+        else:
+            update = self.mixer.forward(h, ctx, binding)
+            if self.feed_forward is not None:
+                h = self.ff_norm.add_norm(hidden, update, ctx.dtype)
         if self.feed_forward is not None:
-            h = self.ff_norm.add_norm(hidden, update, ctx.dtype)
             if self.side is not None and hasattr(self.feed_forward, "last_bias"):
                 # the side input adds the update to the stream anyway: the last bias rides along
                 update, bias = self.feed_forward.forward(h, ctx, add_bias=False), self.feed_forward.last_bias

@@ -79,6 +79,7 @@ class BiasedDense(Part):
     the bias in the same pass (``forward(..., add_bias=True)`` adds it at once)."""
 
     graph_safe = True
+    accepts_pending_norm = True
 
     def __init__(self, width: int, inner: int, activation: str = "gelu_erf") -> None:
         self.width, self.inner, self.activation = int(width), int(inner), activation

@@ -39,6 +39,10 @@ class LatentAttention(Part):
     """
 
     graph_safe = True
+    #: The output projection may carry the caller's residual add and norm (``finish``, see ``Part``);
+    #: it is not chained to the kernels before it, which are library products and a copy.
+    fuses_last_linear = True
+    chains_last_linear = False
     #: Set to False to keep bfloat16 steps on the general (float32-arithmetic) kernel; tests compare the two.
     USE_TENSOR_CORES = True
 
@@ -126,7 +130,7 @@ class LatentAttention(Part):
             splits = int(max(1, min(16, places // (len(work_seq) * columns), longest // 128)))
         ctx.scratch[seq_name] = splits
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding, finish=None) -> torch.Tensor:
         group = ctx.groups[binding.group]
         pool = group.k_pool[binding.index]
         tokens = x.shape[0]
@@ -151,4 +155,4 @@ class LatentAttention(Part):
             group.page_size, self.window or 0, self.scale, ctx.status, **extra)
         values = torch.bmm(attended, self.uv_t)                                # [heads, tokens, vdim]
         merged = values.transpose(0, 1).reshape(tokens, self.heads * self.vdim)
-        return gemm.linear(merged, self.o)
+        return finish(merged, self.o) if finish is not None else gemm.linear(merged, self.o)

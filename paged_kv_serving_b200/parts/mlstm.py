@@ -31,6 +31,9 @@ class MLSTM(Part):
     """
 
     graph_safe = True
+    #: The output projection may carry the caller's residual add and norm (``finish``, see ``Part``).
+    fuses_last_linear = True
+    chains_last_linear = False
 
     def __init__(self, width: int, heads: int, dim: int, vdim: int, gate_cap: float, eps: float) -> None:
         if dim > 1024:
@@ -63,7 +66,7 @@ class MLSTM(Part):
         return {"mlstm_S": StateRequest((self.heads, self.dim, self.vdim)), "mlstm_n": StateRequest((self.heads, self.dim)),
                 "mlstm_m": StateRequest((self.heads,))}
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding, finish=None) -> torch.Tensor:
         # the gates' pre-activations and everything else that enters the recurrence stay float32
         proj = gemm.linear(x, self.fused, out_dtype=torch.float32)
         states = ctx.states
@@ -71,4 +74,4 @@ class MLSTM(Part):
                               states[binding.extra["mlstm_S"]], states[binding.extra["mlstm_n"]],
                               states[binding.extra["mlstm_m"]], ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.STATE_SLOTS),
                               self.heads, self.dim, self.vdim, ctx.dtype)
-        return gemm.linear(out, self.o)
+        return finish(out, self.o) if finish is not None else gemm.linear(out, self.o)
