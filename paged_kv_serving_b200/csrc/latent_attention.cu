@@ -321,7 +321,9 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attention_mma_kernel(const 
   {
     const Q* q_lat = reinterpret_cast<const Q*>(p.q_lat);
     const int half = p.rot_dims >> 1;
-    for (int idx = threadIdx.x; idx < LM_BM * dk; idx += LM_THREADS) {
+    // (only the 16-row tiles that hold a valid row are ever read: a decode entry stages one tile, not the block's all)
+    const int rows_staged = min(LM_BM, (rows_valid + 15) & ~15);
+    for (int idx = threadIdx.x; idx < rows_staged * dk; idx += LM_THREADS) {
       const int row = idx / dk, d = idx - row * dk;
       float v = 0.0f;
       if (row < rows_valid) {

@@ -5,7 +5,9 @@
 //   a_t = exp(f_t + m_{t-1} - m_t),  b_t = exp(i_t - m_t)
 //   S_t = a_t S_{t-1} + b_t k_t v_t^T,   n_t = a_t n_{t-1} + b_t k_t
 //   o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)
-// Everything here is float32: the projections arrive as float32, the state is float32.
+// Everything here is float32: the projections arrive as float32, the state is float32. S is held
+// column by column, [vdim][dim] per (request, head): the lanes that own a column read and write its
+// `dim` entries as one contiguous run.
 //
 // Three kernels.
 // `gates`: one warp per (entry, head). The recurrence of m is a chain of maps x -> max(x + f, i),
@@ -112,7 +114,7 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, 
     for (int r = 0; r < R; ++r) {
       const int d = p + P * r;
       float v = 0.0f;
-      if (d < dim && column < vdim) v = s_mine[(size_t)d * vdim + column];
+      if (d < dim && column < vdim) v = s_mine[(size_t)column * dim + d];
       else if (d < dim && column == vdim) v = n_mine[d];
       sv[c][r] = v;
     }
@@ -206,7 +208,7 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, 
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const int d = p + P * r;
-      if (d < dim && column < vdim) s_mine[(size_t)d * vdim + column] = sv[c][r];
+      if (d < dim && column < vdim) s_mine[(size_t)column * dim + d] = sv[c][r];
       else if (d < dim && column == vdim) n_mine[d] = sv[c][r];
     }
   }

@@ -145,14 +145,14 @@ def mlstm(proj: torch.Tensor, offsets: dict[str, int], i_bias: torch.Tensor, f_b
     """The mLSTM recurrence over a ragged batch. ``proj`` float32 ``[tokens, ld]`` holds the
     projections q, k ``[heads, dim]``, v, g ``[heads, vdim]`` and the two gates' pre-activations
     ``[heads]`` at ``offsets`` ("q", "k", "v", "g", "i", "f"). States (float32): ``s_state [slots,
-    heads, dim, vdim]``, ``n_state [slots, heads, dim]``, ``m_state [slots, heads]``. Returns the
+    heads, vdim, dim]`` (column by column), ``n_state [slots, heads, dim]``, ``m_state [slots, heads]``. Returns the
     heads' outputs after their unit norm, the norm's weight and the output gate, ``[tokens, heads * vdim]``."""
     _need(proj, torch.float32, "proj")
     for name, t in (("s_state", s_state), ("n_state", n_state), ("m_state", m_state), ("i_bias", i_bias), ("f_bias", f_bias),
                     ("norm_weight", norm_weight)):
         _need(t, torch.float32, name)
     tokens, ld = proj.shape
-    if s_state.shape[1:] != (heads, dim, vdim) or n_state.shape[1:] != (heads, dim) or m_state.shape[1:] != (heads,):
+    if s_state.shape[1:] != (heads, vdim, dim) or n_state.shape[1:] != (heads, dim) or m_state.shape[1:] != (heads,):
         raise ValueError("mlstm: the states do not fit heads, dim and vdim")
     if norm_weight.numel() != heads * vdim or i_bias.numel() != heads or f_bias.numel() != heads:
         raise ValueError("mlstm: a vector does not fit the head count")

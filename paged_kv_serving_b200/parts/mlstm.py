@@ -63,7 +63,7 @@ class MLSTM(Part):
         self.norm, self.i_b, self.f_b = params["norm"], params["i_b"], params["f_b"]
 
     def state_requests(self) -> dict[str, StateRequest]:
-        return {"mlstm_S": StateRequest((self.heads, self.dim, self.vdim)), "mlstm_n": StateRequest((self.heads, self.dim)),
+        return {"mlstm_S": StateRequest((self.heads, self.vdim, self.dim)), "mlstm_n": StateRequest((self.heads, self.dim)),
                 "mlstm_m": StateRequest((self.heads,))}
 
     def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding, finish=None) -> torch.Tensor:

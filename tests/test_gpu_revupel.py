@@ -473,7 +473,7 @@ def test_mlstm_kernels_remember_a_token_from_far_back():
     zeros = torch.zeros(heads, device="cuda")
     results = []
     for cuts in ([tokens], [1] * 10 + [tokens - 10], [2, 50, 3, tokens - 55]):
-        S = torch.zeros((2, heads, dim, vdim), device="cuda")
+        S = torch.zeros((2, heads, vdim, dim), device="cuda")
         n = torch.zeros((2, heads, dim), device="cuda")
         m = torch.zeros((2, heads), device="cuda")
         rows, at = [], 0
