@@ -87,7 +87,8 @@ __device__ __forceinline__ void ml_cp_async16(float* smem, const float* gmem) {
 // A group of P lanes owns ML_C columns, each lane R entries of every one of them: P * R >= dim,
 // P a power of two <= 32. Column `vdim` is the normaliser n (its value is 1 for every token; its
 // state lives in n_state and its readout n . q goes to `dots`).
-template <int R, int ML_C>
+// EXACT: dim == P * R, so no entry of a lane lies beyond the column and the inner loops carry no guards.
+template <int R, int ML_C, bool EXACT>
 __global__ void __launch_bounds__(128)
 mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, float q_scale,
                   const float* __restrict__ coef, float* __restrict__ s_state, float* __restrict__ n_state,
@@ -163,14 +164,16 @@ mlstm_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, 
     const float* vs = qs + chunk * dim;
     const float* cs = vs + chunk * per_block;
     const int n = min(chunk, count - first);
-    for (int t = 0; t < n; ++t) {
+    const float* kt = ks + p;
+    const float* qt = qs + p;
+    for (int t = 0; t < n; ++t, kt += dim, qt += dim) {
       const float a = cs[2 * t], b = cs[2 * t + 1];
       float kk[R], qq[R];
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        const int d = p + P * r;
-        kk[r] = d < dim ? ks[t * dim + d] : 0.0f;
-        qq[r] = d < dim ? qs[t * dim + d] : 0.0f;
+        const bool in = EXACT || p + P * r < dim;
+        kk[r] = in ? kt[P * r] : 0.0f;
+        qq[r] = in ? qt[P * r] : 0.0f;
       }
       float num[ML_C];
 #pragma unroll
@@ -265,7 +268,7 @@ PKV_EXPORT int pkv_mlstm(const float* proj, int ld, int q_off, int k_off, int v_
   const int R = dim <= 256 ? 8 : 32;
   // columns per group of lanes (registers: ML_C * R state entries a lane). Two columns a group, which doubles
   // the blocks of a single long prompt, measured slower than four (keys and queries are staged twice as often).
-  const int ML_C = dim <= 256 ? 4 : 2;
+  const int ML_C = dim <= 256 ? 4 : 1;
   int P = 1;
   while (P * R < dim) P <<= 1;
   const int per_block = (128 / P) * ML_C;
@@ -276,13 +279,17 @@ PKV_EXPORT int pkv_mlstm(const float* proj, int ld, int q_off, int k_off, int v_
   float* dots = o + (size_t)tokens * heads * vdim;
   const int vec4 = (dim % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && chunk % 2 == 0) ? 1 : 0;
   dim3 grid((vdim + 1 + per_block - 1) / per_block, heads, seqs);
-  if (R == 8) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_scan_kernel<8, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    mlstm_scan_kernel<8, 4><<<grid, 128, smem, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, n_state, seq_starts,
+  if (R == 8 && P * R == dim) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_scan_kernel<8, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    mlstm_scan_kernel<8, 4, true><<<grid, 128, smem, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, n_state, seq_starts,
+                                                       state_slots, o, dots, heads, dim, vdim, P, chunk, vec4);
+  } else if (R == 8) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_scan_kernel<8, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    mlstm_scan_kernel<8, 4, false><<<grid, 128, smem, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, n_state, seq_starts,
                                                  state_slots, o, dots, heads, dim, vdim, P, chunk, vec4);
   } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_scan_kernel<32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    mlstm_scan_kernel<32, 2><<<grid, 128, smem, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, n_state, seq_starts,
+    if (smem > 48 * 1024) cudaFuncSetAttribute(mlstm_scan_kernel<32, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    mlstm_scan_kernel<32, 1, false><<<grid, 128, smem, s>>>(proj, ld, q_off, k_off, v_off, q_scale, coef, s_state, n_state, seq_starts,
                                                   state_slots, o, dots, heads, dim, vdim, P, chunk, vec4);
   }
   const long long rows = (long long)tokens * heads;
