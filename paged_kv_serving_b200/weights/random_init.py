@@ -37,8 +37,9 @@ def random_tensors(specs: dict[str, ParamSpec], seed: int, std: float | Callable
         if spec.kind == "int_table":
             out[name] = torch.zeros(spec.shape, dtype=torch.int32)
         elif spec.kind == "vector":
-            values = (1.0 + norm_jitter * rng.standard_normal(spec.shape)).astype(np.float32)
-            out[name] = torch.from_numpy(values)
+            # (np.asarray: a tensor without axes, one number, comes back from the generator as a scalar)
+            values = np.asarray(1.0 + norm_jitter * rng.standard_normal(spec.shape), dtype=np.float32)
+            out[name] = torch.from_numpy(values.copy())
         else:
             scale = std(name) if callable(std) else std
             values = (rng.standard_normal(spec.shape) * scale).astype(np.float32)
