@@ -66,8 +66,14 @@ CONFIG_C = {
     "loop": {"start": 0, "stop": 1, "times": 3},
     "layers": [_layer(_attention(2, 8, 8, 8, 8, 16), _dense(32))],
 }
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
-PAGE = {"A": 8, "B": 4, "C": 16}
+#: "D": sizes that are no multiples of 8, some of them odd (nothing may rest on alignment).
+CONFIG_D = {
+    "architecture": "Revupel", "vocab": 77, "width": 100, "norm": {"eps": 1e-5}, "canon": {"taps": 3}, "token_side": {"dim": 3},
+    "layers": [_layer(_attention(3, 10, 6, 7, 18, 21, rot_dims=4), _moe(3, 2, 10, 6)), _layer(_mlstm(3, 10, 7, 11.0), _dense(30)),
+               _layer(_attention(2, 9, 2, 5, 11, 13), _moe(5, 3, 9, 0))],
+}
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
+PAGE = {"A": 8, "B": 4, "C": 16, "D": 16}
 
 
 def _specs(config):
