@@ -11,7 +11,8 @@ Behaviour follows the reference's single-group manager
 compute, publishing of full pages, all-or-nothing reservation with eviction and copy-on-write,
 forking by sharing, and release on finish, abort or preemption. What is new here: several groups,
 the window rule (pages that every later query has moved past are given back between steps and
-their table entry becomes ``NULL_PAGE``), and a slot for per-request state of fixed size.
+their table entry becomes ``NULL_PAGE``; a group may keep a sequence's first positions readable,
+whose pages then stay), and a slot for per-request state of fixed size.
 The prefix cache is used only when every group keeps every key and no mixer has a state of its
 own, since a cached prefix must be complete in every group.
 """
@@ -36,6 +37,8 @@ class GroupSpec:
     head_dim: int
     window: int | None = None
     values: bool = True           # False: one cached vector per position, no value pool
+    value_dim: int | None = None  # size of a value head when it is not that of a key head
+    keep_first: int = 0           # with a window: positions below this stay readable for good
 
 
 @dataclass(frozen=True, slots=True)
@@ -54,12 +57,16 @@ def plan_groups(cache_entries: list[tuple[int, object]]) -> tuple[list[GroupSpec
     states: list[tuple[int, object]] = []
     for number, request in cache_entries:
         if isinstance(request, PagedKVRequest):
-            grouped.setdefault((request.n_kv_heads, request.head_dim, request.window, request.values), []).append(number)
+            value_dim = request.value_dim if request.value_dim not in (None, request.head_dim) else None
+            keep_first = request.keep_first if request.window is not None else 0
+            grouped.setdefault((request.n_kv_heads, request.head_dim, request.window, request.values, value_dim,
+                                keep_first), []).append(number)
         elif isinstance(request, StateRequest):
             states.append((number, request))
         else:
             raise TypeError(f"unknown cache request {request!r}")
-    groups = [GroupSpec(tuple(entries), kv, hd, window, values) for (kv, hd, window, values), entries in grouped.items()]
+    groups = [GroupSpec(tuple(entries), kv, hd, window, values, value_dim, keep_first)
+              for (kv, hd, window, values, value_dim, keep_first), entries in grouped.items()]
     return groups, states
 
 
@@ -237,7 +244,9 @@ class KVCacheManager:
 
         A query at position ``p`` of a group with window ``W`` reads keys ``p-W+1 .. p``; the next
         query sits at ``num_computed_tokens`` or later, so every position up to
-        ``num_computed_tokens - W`` is out of reach. Returns the number of pages given back.
+        ``num_computed_tokens - W`` is out of reach, except the first ``keep_first`` positions of
+        a group that keeps them: the pages that hold any of those stay. Returns the number of
+        pages given back.
         """
         released = 0
         if not self._windowed:
@@ -250,7 +259,8 @@ class KVCacheManager:
             # pages are given back from the front, so the ones already gone form a prefix: walk
             # back from the newest dead page until one of them is met
             i = min(dead_pages, len(table)) - 1
-            while i >= 0 and table[i] != NULL_PAGE:
+            kept_pages = -(-spec.keep_first // self.block_size)         # pages that hold kept first positions
+            while i >= kept_pages and table[i] != NULL_PAGE:
                 allocator.release(table[i])
                 table[i] = NULL_PAGE
                 released += 1

@@ -20,7 +20,8 @@ namespace pkv {
 template <typename W>
 __global__ void embedding_gather_kernel(const W* __restrict__ table, const int32_t* __restrict__ ids,
                                         float* __restrict__ out, int d, int vocab, int* __restrict__ status,
-                                        const int32_t* __restrict__ fed_back, const int32_t* __restrict__ fed_back_at) {
+                                        const int32_t* __restrict__ fed_back, const int32_t* __restrict__ fed_back_at,
+                                        float scale) {
   dependents_may_launch();
   wait_for_prior_kernels();
   const int t = blockIdx.x;
@@ -35,7 +36,7 @@ __global__ void embedding_gather_kernel(const W* __restrict__ table, const int32
   }
   const W* row = table + (size_t)id * d;
   float* dst = out + (size_t)t * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_float(row[i]);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = to_float(row[i]) * scale;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -350,7 +351,7 @@ using namespace pkv;
 
 PKV_EXPORT int pkv_embedding_gather(const void* table, int table_dtype, const int32_t* ids, float* out,
                                     int n_tokens, int d, int vocab, int* status, const int32_t* fed_back,
-                                    const int32_t* fed_back_at, void* stream) {
+                                    const int32_t* fed_back_at, float scale, void* stream) {
   if (n_tokens <= 0) return 0;
   if (d <= 0 || vocab <= 0) return PKV_ERR_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
@@ -358,10 +359,10 @@ PKV_EXPORT int pkv_embedding_gather(const void* table, int table_dtype, const in
   // the first kernel of a step follows a copy from the host, not a kernel: an ordinary launch
   if (table_dtype == PKV_F32)
     return launch_kernel(embedding_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, false, 0,
-                         (const float*)table, ids, out, d, vocab, status, fed_back, fed_back_at);
+                         (const float*)table, ids, out, d, vocab, status, fed_back, fed_back_at, scale);
   if (table_dtype == PKV_BF16)
     return launch_kernel(embedding_gather_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, false, 0,
-                         (const bf16*)table, ids, out, d, vocab, status, fed_back, fed_back_at);
+                         (const bf16*)table, ids, out, d, vocab, status, fed_back, fed_back_at, scale);
   return PKV_ERR_DTYPE;
 }
 

@@ -6,7 +6,8 @@
 
 namespace pkv {
 
-enum Activation { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_RELU_SQUARED = 3, ACT_SIGMOID = 4 };
+enum Activation { ACT_NONE = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_RELU_SQUARED = 3, ACT_SIGMOID = 4, ACT_SILU = 5 };
+constexpr int ACT_LAST = ACT_SILU;
 
 __device__ __forceinline__ float activate(float z, int act) {
   switch (act) {
@@ -17,6 +18,7 @@ __device__ __forceinline__ float activate(float z, int act) {
     }
     case ACT_RELU_SQUARED: { const float r = fmaxf(z, 0.0f); return r * r; }
     case ACT_SIGMOID: return 1.0f / (1.0f + expf(-z));
+    case ACT_SILU: return z / (1.0f + expf(-z));
     default: return z;
   }
 }
@@ -62,35 +64,44 @@ __global__ void act_times_table_kernel(const X* __restrict__ z, const X* __restr
   out[i] = from_float<X>(activate(to_float(z[i]), act) * e);
 }
 
-// Router: softmax over the experts' logits of a token, the `top` largest scores kept (the lower
-// index wins a tie), all others zero. weights[t, e] is the score of a chosen expert, not renormalised.
-__global__ void route_top_kernel(const float* __restrict__ logits, int ld, float* __restrict__ weights, int tokens,
-                                 int experts, int top) {
+// Router: the `top` largest logits of a token are chosen (the lower index wins a tie). Their
+// weights are their softmax scores over all experts as they are, or, with `renormalise`, the
+// softmax over the chosen logits only; every other expert's weight is zero. `bias` (or none) is
+// added to the logits first.
+__global__ void route_top_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias,
+                                 float* __restrict__ weights, int tokens, int experts, int top, int renormalise) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= tokens) return;
   const float* z = logits + (size_t)t * ld;
   float* w = weights + (size_t)t * experts;
   float m = -INFINITY;
-  for (int e = 0; e < experts; ++e) m = fmaxf(m, z[e]);
+  for (int e = 0; e < experts; ++e) m = fmaxf(m, z[e] + (bias ? bias[e] : 0.0f));
   float sum = 0.0f;
-  for (int e = 0; e < experts; ++e) sum += expf(z[e] - m);
+  if (!renormalise)
+    for (int e = 0; e < experts; ++e) sum += expf(z[e] + (bias ? bias[e] : 0.0f) - m);
   for (int e = 0; e < experts; ++e) w[e] = 0.0f;
   // pick `top` times the largest logit not picked yet; a picked expert's weight is > 0
   float last = INFINITY;
   int last_e = -1;
+  float chosen_sum = 0.0f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int best_e = -1;
     for (int e = 0; e < experts; ++e) {
-      const float v = z[e];
+      const float v = z[e] + (bias ? bias[e] : 0.0f);
       const bool after_last = v < last || (v == last && e > last_e);   // order: score down, index up
       if (after_last && v > best) { best = v; best_e = e; }
     }
     if (best_e < 0) break;
-    w[best_e] = expf(best - m) / sum;
+    const float p = expf(best - m);
+    w[best_e] = p;
+    chosen_sum += p;
     last = best;
     last_e = best_e;
   }
+  const float denom = renormalise ? chosen_sum : sum;
+  for (int e = 0; e < experts; ++e)
+    if (w[e] != 0.0f) w[e] = w[e] / denom;
 }
 
 // up[t, :] holds the up-projections of all routed experts ([experts][ff]) and then of the shared
@@ -172,6 +183,73 @@ __global__ void expert_act_bf16x8_kernel(const bf16* __restrict__ up, int ld, co
   store8(out + (size_t)t * cols + c, v);
 }
 
+
+// Gated experts: gu[t, :] holds the gate projections of all routed experts ([experts][ff]) and of
+// the shared expert ([shared_ff]) and, `up_at` columns further on, the up projections in the same
+// order. out[t, c] = scale * act(gate) * up with the router's weight of the column's expert as
+// scale (1 for the shared expert); an expert the token does not use gives exact zeros.
+template <typename X>
+__global__ void expert_gated_act_kernel(const X* __restrict__ gu, int ld, int up_at, const float* __restrict__ weights,
+                                        X* __restrict__ out, int tokens, int experts, int ff, int shared_ff, int act) {
+  const int cols = experts * ff + shared_ff;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * cols) return;
+  const int t = (int)(i / cols), c = (int)(i - (long long)t * cols);
+  const float scale = c < experts * ff ? weights[(size_t)t * experts + c / ff] : 1.0f;
+  float v = 0.0f;
+  if (scale != 0.0f) {
+    const X* row = gu + (size_t)t * ld;
+    v = scale * (activate(to_float(row[c]), act) * to_float(row[up_at + c]));
+  }
+  out[(size_t)t * cols + c] = from_float<X>(v);
+}
+
+__global__ void expert_gated_act_bf16x8_kernel(const bf16* __restrict__ gu, int ld, int up_at,
+                                               const float* __restrict__ weights, bf16* __restrict__ out, int tokens,
+                                               int experts, int ff, int shared_ff, int act) {
+  const int cols = experts * ff + shared_ff;
+  const int per_row = cols >> 3;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * per_row) return;
+  const int t = (int)(i / per_row), c = (int)(i - (long long)t * per_row) << 3;
+  const float scale = c < experts * ff ? weights[(size_t)t * experts + c / ff] : 1.0f;
+  Pack8 v;
+  if (scale != 0.0f) {
+    v = load8(gu + (size_t)t * ld + c);
+    const Pack8 u = load8(gu + (size_t)t * ld + up_at + c);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v.v[k] = scale * (activate(v.v[k], act) * u.v[k]);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v.v[k] = 0.0f;
+  }
+  store8(out + (size_t)t * cols + c, v);
+}
+
+// The residual step of a block that normalises a sublayer's output, not its input:
+//   hidden[r] += delta[r] / sqrt(mean(delta[r]^2) + eps) * weight;   out[r] = hidden[r] in the type of out
+// One block a row; the row waits in shared memory between the two passes.
+template <typename D, typename O>
+__global__ void norm_residual_kernel(float* __restrict__ hidden, const D* __restrict__ delta, const float* __restrict__ weight,
+                                     float eps, O* __restrict__ out, int d) {
+  extern __shared__ float nr_smem[];   // d floats + 32 scratch
+  float* row = nr_smem;
+  float* scratch = nr_smem + d;
+  const size_t at = (size_t)blockIdx.x * d;
+  float sq = 0.0f;
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float v = to_float(delta[at + c]);
+    row[c] = v;
+    sq = fmaf(v, v, sq);
+  }
+  sq = block_sum(sq, scratch);
+  const float inv = 1.0f / sqrtf(sq / (float)d + eps);
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float v = hidden[at + c] + row[c] * inv * weight[c];
+    hidden[at + c] = v;
+    if (out) out[at + c] = from_float<O>(v);
+  }
+}
 
 // Dot product of `n` weights with float values in shared memory; 16-byte loads for bfloat16 rows
 // that start on 16-byte boundaries (n a multiple of 8), lane-strided otherwise.
@@ -255,7 +333,7 @@ PKV_EXPORT int pkv_bias_act(const void* x, int x_dtype, const float* bias, void*
                             int cols, int act, void* stream) {
   const long long total = rows * cols;
   if (total <= 0) return 0;
-  if (act < 0 || act > 4) return PKV_ERR_SIZE;
+  if (act < 0 || act > ACT_LAST) return PKV_ERR_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
   if (x_dtype == PKV_BF16 && out_dtype == PKV_BF16 && cols % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
     bias_act_bf16x8_kernel<<<blocks_for(total / 8, 256), 256, 0, s>>>((const bf16*)x, bias, (bf16*)out, total / 8, cols, act);
@@ -289,7 +367,7 @@ PKV_EXPORT int pkv_act_times_table(const void* z, const void* table, int dtype, 
                                    const int32_t* fed_back, const int32_t* fed_back_at, int* status, void* stream) {
   const long long total = (long long)tokens * n;
   if (total <= 0) return 0;
-  if (col0 < 0 || col0 + n > table_cols || act < 0 || act > 4) return PKV_ERR_SIZE;
+  if (col0 < 0 || col0 + n > table_cols || act < 0 || act > ACT_LAST) return PKV_ERR_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == PKV_F32) {
     act_times_table_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)z, (const float*)table, table_cols,
@@ -303,18 +381,69 @@ PKV_EXPORT int pkv_act_times_table(const void* z, const void* table, int dtype, 
   return launch_status();
 }
 
-PKV_EXPORT int pkv_route_top(const float* logits, int ld, float* weights, int tokens, int experts, int top, void* stream) {
+PKV_EXPORT int pkv_route_top(const float* logits, int ld, const float* bias, float* weights, int tokens, int experts, int top,
+                             int renormalise, void* stream) {
   if (tokens <= 0) return 0;
   if (experts < 1 || top < 1 || top > experts || ld < experts) return PKV_ERR_SIZE;
-  route_top_kernel<<<blocks_for(tokens, 128), 128, 0, (cudaStream_t)stream>>>(logits, ld, weights, tokens, experts, top);
+  route_top_kernel<<<blocks_for(tokens, 128), 128, 0, (cudaStream_t)stream>>>(logits, ld, bias, weights, tokens, experts, top,
+                                                                              renormalise);
   return launch_status();
+}
+
+PKV_EXPORT int pkv_expert_gated_act(const void* gu, int dtype, int ld, int up_at, const float* weights, void* out, int tokens,
+                                    int experts, int ff, int shared_ff, int act, void* stream) {
+  const long long cols = (long long)experts * ff + shared_ff;
+  const long long total = (long long)tokens * cols;
+  if (total <= 0) return 0;
+  if (experts < 0 || ff < 0 || shared_ff < 0 || act < 0 || act > ACT_LAST || up_at < cols || ld < up_at + cols) return PKV_ERR_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == PKV_F32) {
+    expert_gated_act_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)gu, ld, up_at, weights, (float*)out,
+                                                                          tokens, experts, ff, shared_ff, act);
+  } else if (dtype == PKV_BF16 && ff % 8 == 0 && shared_ff % 8 == 0 && ld % 8 == 0 && up_at % 8 == 0 &&
+             ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
+    expert_gated_act_bf16x8_kernel<<<blocks_for(total / 8, 256), 256, 0, s>>>((const bf16*)gu, ld, up_at, weights, (bf16*)out,
+                                                                               tokens, experts, ff, shared_ff, act);
+  } else if (dtype == PKV_BF16) {
+    expert_gated_act_kernel<bf16><<<blocks_for(total, 256), 256, 0, s>>>((const bf16*)gu, ld, up_at, weights, (bf16*)out,
+                                                                         tokens, experts, ff, shared_ff, act);
+  } else {
+    return PKV_ERR_DTYPE;
+  }
+  return launch_status();
+}
+
+PKV_EXPORT int pkv_norm_residual(float* hidden, const void* delta, int delta_dtype, const float* weight, float eps, void* out,
+                                 int out_dtype, int rows, int d, void* stream) {
+  if (rows <= 0) return 0;
+  if (d <= 0) return PKV_ERR_SIZE;
+  const size_t smem = (size_t)(d + 32) * sizeof(float);
+  if (smem > 200 * 1024) return PKV_ERR_LIMIT;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+#define PKV_NR(D, O)                                                                                                     \
+  do {                                                                                                                   \
+    if (smem > 48 * 1024) {                                                                                              \
+      cudaError_t e = cudaFuncSetAttribute(norm_residual_kernel<D, O>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return (int)e;                                                                               \
+    }                                                                                                                    \
+    norm_residual_kernel<D, O><<<rows, threads, smem, s>>>(hidden, (const D*)delta, weight, eps, (O*)out, d);            \
+    return launch_status();                                                                                              \
+  } while (0)
+  if (!out) out_dtype = PKV_F32;
+  if (delta_dtype == PKV_F32 && out_dtype == PKV_F32) PKV_NR(float, float);
+  if (delta_dtype == PKV_F32 && out_dtype == PKV_BF16) PKV_NR(float, bf16);
+  if (delta_dtype == PKV_BF16 && out_dtype == PKV_BF16) PKV_NR(bf16, bf16);
+  if (delta_dtype == PKV_BF16 && out_dtype == PKV_F32) PKV_NR(bf16, float);
+#undef PKV_NR
+  return PKV_ERR_DTYPE;
 }
 
 PKV_EXPORT int pkv_expert_act(const void* up, int dtype, int ld, const float* weights, const float* gate, int gate_ld,
                               void* out, int tokens, int experts, int ff, int shared_ff, int act, void* stream) {
   const long long total = (long long)tokens * ((long long)experts * ff + shared_ff);
   if (total <= 0) return 0;
-  if (experts < 0 || ff < 0 || shared_ff < 0 || act < 0 || act > 4) return PKV_ERR_SIZE;
+  if (experts < 0 || ff < 0 || shared_ff < 0 || act < 0 || act > ACT_LAST) return PKV_ERR_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == PKV_F32) {
     expert_act_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)up, ld, weights, gate, gate_ld,
@@ -338,7 +467,7 @@ PKV_EXPORT int pkv_token_side(float* hidden, const void* delta, int delta_dtype,
                               int dim, int act, const int32_t* fed_back, const int32_t* fed_back_at, int* status,
                               void* stream) {
   if (tokens <= 0) return 0;
-  if (width < 1 || dim < 1 || col0 < 0 || col0 + dim > table_cols || act < 0 || act > 4) return PKV_ERR_SIZE;
+  if (width < 1 || dim < 1 || col0 < 0 || col0 + dim > table_cols || act < 0 || act > ACT_LAST) return PKV_ERR_SIZE;
   const size_t smem = (size_t)(2 * width + dim + 32) * sizeof(float);
   if (smem > 200 * 1024) return PKV_ERR_LIMIT;
   cudaStream_t s = (cudaStream_t)stream;

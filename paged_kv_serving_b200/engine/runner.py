@@ -34,8 +34,8 @@ __all__ = ["CacheStorage", "ModelRunner", "StepResult"]
 
 class CacheStorage:
     """Device memory of the cache: per page group one key pool and one value pool shaped
-    ``[layers of the group, pages, kv heads, page_size, head_dim]`` (no value pool for a group
-    without values), and per state entry a tensor ``[slots + 1, *shape]``: the last slot belongs to
+    ``[layers of the group, pages, kv heads, page_size, head_dim]`` (the value pool with the
+    group's value size where that differs; no value pool for a group without values), and per state entry a tensor ``[slots + 1, *shape]``: the last slot belongs to
     no request, the stand-in entries that pad a captured step to its size class use it."""
 
     def __init__(self, groups: list[GroupSpec], state_entries: list, *, num_blocks: int, block_size: int,
@@ -48,8 +48,9 @@ class CacheStorage:
         self.location: dict[int, tuple[int, int]] = {}
         for g, spec in enumerate(groups):
             shape = (len(spec.entries), num_blocks, spec.n_kv_heads, block_size, spec.head_dim)
+            v_shape = (*shape[:-1], spec.value_dim or spec.head_dim)
             self.k_pools.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=device) if spec.values else None)
+            self.v_pools.append(torch.zeros(v_shape, dtype=dtype, device=device) if spec.values else None)
             for index, entry in enumerate(spec.entries):
                 self.location[entry] = (g, index)
         self.states: list[torch.Tensor] = []
@@ -70,8 +71,12 @@ class CacheStorage:
     def copy_page(self, group: int, source: int, destination: int) -> None:
         if source == destination:
             raise ValueError("a page is never copied onto itself")
-        values = self.v_pools[group]
-        ops.copy_page(self.k_pools[group], values if values is not None else self.k_pools[group], source, destination)
+        keys, values = self.k_pools[group], self.v_pools[group]
+        if values is not None and values.shape != keys.shape:      # value heads of another size: a launch per pool
+            ops.copy_page(keys, keys, source, destination)
+            ops.copy_page(values, values, source, destination)
+            return
+        ops.copy_page(keys, values if values is not None else keys, source, destination)
 
     def copy_state(self, source_slot: int, destination_slot: int) -> None:
         for state in self.states:

@@ -3,5 +3,6 @@
 from paged_kv_serving_b200.models.layout import LayerCall, ModelLayout, collect_param_specs
 from paged_kv_serving_b200.models.llama_toy_decoder import LlamaToyDecoder
 from paged_kv_serving_b200.models.revupel import Revupel
+from paged_kv_serving_b200.models.tiburax import Tiburax
 
-__all__ = ["LayerCall", "LlamaToyDecoder", "ModelLayout", "Revupel", "collect_param_specs"]
+__all__ = ["LayerCall", "LlamaToyDecoder", "ModelLayout", "Revupel", "Tiburax", "collect_param_specs"]

@@ -97,8 +97,10 @@ def _fn(lib_name: str, fn_name: str, argtypes: list):
 
 
 def embedding_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor,
-                     fed_back: torch.Tensor | None = None, fed_back_at: torch.Tensor | None = None) -> torch.Tensor:
-    """``table[ids]`` widened to float32. An id outside the table sets ``status[0]`` to 1.
+                     fed_back: torch.Tensor | None = None, fed_back_at: torch.Tensor | None = None,
+                     scale: float = 1.0) -> torch.Tensor:
+    """``table[ids] * scale`` widened to float32 (the product is a float32 one). An id outside the
+    table sets ``status[0]`` to 1.
     With ``fed_back`` (int32 ids on the device) and ``fed_back_at`` (one int32 per token), a token
     whose ``fed_back_at`` is not negative takes ``fed_back[fed_back_at]`` as its id."""
     _need(table, None, "table"); _need(ids, torch.int32, "ids"); _need(status, torch.int32, "status")
@@ -111,9 +113,9 @@ def embedding_gather(table: torch.Tensor, ids: torch.Tensor, status: torch.Tenso
     vocab, d = table.shape
     out = _empty((ids.numel(), d), torch.float32, table.device)
     fn = _fn("elementwise", "pkv_embedding_gather",
-             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p])
     _check(fn(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), ids.numel(), d, vocab,
-              _ptr(status), _ptr(fed_back), _ptr(fed_back_at), _stream()), "embedding_gather")
+              _ptr(status), _ptr(fed_back), _ptr(fed_back_at), float(scale), _stream()), "embedding_gather")
     return out
 
 

@@ -23,7 +23,7 @@ from __future__ import annotations
 
 import torch
 
-__all__ = ["StepArena", "active", "empty"]
+__all__ = ["StepArena", "active", "empty", "empty_for_step"]
 
 _ALIGN = 256
 _MIN_BLOCK = 64 << 20
@@ -97,6 +97,14 @@ class StepArena:
         itemsize = torch.empty((), dtype=dtype).element_size() if dtype not in _ITEMSIZE else _ITEMSIZE[dtype]
         return self._current.take(count * itemsize)[:count * itemsize].view(dtype).view(tuple(int(s) for s in shape))
 
+    def empty_for_step(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        """Memory that stays valid until the step ends, whichever layer asks for it."""
+        current, self._current = self._current, self.step_slot
+        try:
+            return self.empty(shape, dtype)
+        finally:
+            self._current = current
+
     @property
     def reserved_bytes(self) -> int:
         return self.step_slot.reserved_bytes + sum(s.reserved_bytes for s in self.layer_slots)
@@ -124,4 +132,13 @@ def empty(shape, dtype: torch.dtype, device: torch.device | str) -> torch.Tensor
     arena = _ACTIVE[0]
     if arena is not None and arena.device == torch.device(device):
         return arena.empty(shape, dtype)
+    return torch.empty(tuple(shape), dtype=dtype, device=device)
+
+
+def empty_for_step(shape, dtype: torch.dtype, device: torch.device | str) -> torch.Tensor:
+    """Like ``empty``, for what one layer leaves for layers further on than the next: valid until
+    the step ends."""
+    arena = _ACTIVE[0]
+    if arena is not None and arena.device == torch.device(device):
+        return arena.empty_for_step(shape, dtype)
     return torch.empty(tuple(shape), dtype=dtype, device=device)

@@ -1,6 +1,7 @@
-"""Bindings of the kernels in ``csrc/pointwise.cu``, ``csrc/conv_state.cu``, ``csrc/mlstm.cu`` and
-``csrc/latent_attention.cu``: what mixers with a state of their own, a cached latent, routed
-experts and per-token side inputs need beside the kernels bound in ``ops/__init__.py``.
+"""Bindings of the kernels in ``csrc/pointwise.cu``, ``csrc/conv_state.cu``, ``csrc/mlstm.cu``,
+``csrc/selective_scan.cu``, ``csrc/latent_attention.cu`` and ``csrc/attention_sink.cu``: what mixers
+with a state of their own, a cached latent, a window that keeps the first tokens, routed experts
+and per-token side inputs need beside the kernels bound in ``ops/__init__.py``.
 The same conventions hold: CUDA tensors only, launches on torch's current stream, a refused
 argument raises ``ValueError``, nothing falls back to a library or to the CPU.
 """
@@ -15,12 +16,13 @@ from paged_kv_serving_b200 import ops
 from paged_kv_serving_b200.ops import _check, _fn, _need, _ptr, _stream, dtype_code
 from paged_kv_serving_b200.ops.arena import empty as _empty
 
-__all__ = ["ACTIVATIONS", "act_times_table", "bias_act", "conv_residual", "expert_act", "latent_attention",
+__all__ = ["ACTIVATIONS", "act_times_table", "bias_act", "conv_residual", "expert_act", "expert_gated_act", "norm_residual", "latent_attention",
            "latent_attention_mma", "latent_mma_rows_per_block", "latent_mma_supports", "latent_prepare",
-           "latent_rows_per_block", "mlstm", "residual_add", "route_top", "token_side"]
+           "latent_rows_per_block", "mlstm", "residual_add", "route_top", "token_side", "attention_sink",
+           "attention_sink_rows_per_block", "qkv_prepare", "selective_scan"]
 
 #: activation names of ``bias_act`` / ``act_times_table`` / ``expert_act``
-ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "relu_squared": 3, "sigmoid": 4}
+ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "relu_squared": 3, "sigmoid": 4, "silu": 5}
 
 
 def bias_act(x: torch.Tensor, bias: torch.Tensor | None, act: str, out_dtype: torch.dtype | None = None) -> torch.Tensor:
@@ -73,15 +75,56 @@ def act_times_table(z: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col
     return out
 
 
-def route_top(logits: torch.Tensor, experts: int, top: int) -> torch.Tensor:
-    """Router weights ``[tokens, experts]`` (float32): the softmax score of each of a token's
-    ``top`` best experts, zero elsewhere. ``logits [tokens, >= experts]`` float32 (further columns
-    are ignored)."""
+def route_top(logits: torch.Tensor, experts: int, top: int, bias: torch.Tensor | None = None,
+              renormalise: bool = False) -> torch.Tensor:
+    """Router weights ``[tokens, experts]`` (float32) of each token's ``top`` experts with the
+    largest logits, zero elsewhere: their softmax scores over all experts as they are, or, with
+    ``renormalise``, the softmax over the chosen logits only. ``logits [tokens, >= experts]``
+    float32 (further columns are ignored); ``bias [experts]`` float32 is added to them first."""
     _need(logits, torch.float32, "logits")
     tokens, ld = logits.shape
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != experts:
+            raise ValueError("the router's bias needs one element per expert")
     out = _empty((tokens, experts), torch.float32, logits.device)
-    fn = _fn("pointwise", "pkv_route_top", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(fn(_ptr(logits), ld, _ptr(out), tokens, experts, top, _stream()), "route_top")
+    fn = _fn("pointwise", "pkv_route_top", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(logits), ld, _ptr(bias), _ptr(out), tokens, experts, top, int(bool(renormalise)), _stream()), "route_top")
+    return out
+
+
+def expert_gated_act(gate_up: torch.Tensor, up_at: int, weights: torch.Tensor, experts: int, ff: int, shared_ff: int,
+                     act: str) -> torch.Tensor:
+    """``weights[t, e] * act(gate[t, e * ff + j]) * up[t, e * ff + j]`` for the routed experts'
+    columns and ``act(gate) * up`` for the ``shared_ff`` columns behind them. A row of ``gate_up``
+    holds all gate columns and, ``up_at`` columns further on, all up columns in the same order."""
+    _need(gate_up, None, "gate_up"); _need(weights, torch.float32, "weights")
+    tokens, ld = gate_up.shape
+    cols = experts * ff + shared_ff
+    if up_at < cols or ld < up_at + cols or weights.shape != (tokens, experts):
+        raise ValueError("expert_gated_act: sizes do not fit")
+    out = _empty((tokens, cols), gate_up.dtype, gate_up.device)
+    fn = _fn("pointwise", "pkv_expert_gated_act",
+             [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(gate_up), dtype_code(gate_up.dtype), ld, int(up_at), _ptr(weights), _ptr(out), tokens, experts, ff,
+              shared_ff, ACTIVATIONS[act], _stream()), "expert_gated_act")
+    return out
+
+
+def norm_residual(hidden: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float,
+                  out_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+    """``hidden += delta / sqrt(mean(delta^2) + eps) * weight`` in place (float32 stream) and, with
+    ``out_dtype``, the updated stream in that type: the residual step of a block that normalises
+    a sublayer's output, whose next sublayer reads the stream itself."""
+    _need(hidden, torch.float32, "hidden"); _need(delta, None, "delta"); _need(weight, torch.float32, "weight")
+    rows, d = hidden.shape
+    if delta.shape != hidden.shape or weight.numel() != d:
+        raise ValueError("norm_residual: sizes do not fit")
+    out = _empty((rows, d), out_dtype, hidden.device) if out_dtype is not None else None
+    fn = _fn("pointwise", "pkv_norm_residual",
+             [c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(hidden), _ptr(delta), dtype_code(delta.dtype), _ptr(weight), float(eps), _ptr(out),
+              dtype_code(out_dtype) if out_dtype is not None else 0, rows, d, _stream()), "norm_residual")
     return out
 
 
@@ -109,12 +152,18 @@ def expert_act(up: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor | Non
 
 
 def conv_residual(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, token_seq: torch.Tensor,
-                  seq_starts: torch.Tensor, state_slots: torch.Tensor, weight_t: torch.Tensor | None = None) -> torch.Tensor:
-    """``x + causal_conv(x)`` per channel for a ragged batch, ``weight [width, taps]`` float32 with
-    tap ``taps - 1`` on the token itself; ``state [slots, taps - 1, width]`` (type of ``x``) holds
-    every request's last inputs and is brought up to date. ``weight_t`` (the weights as ``[taps,
-    width]``) lets bfloat16 rows of a width that is a multiple of 8 take the 16-byte kernel."""
-    _need(x, None, "x"); _need(weight, torch.float32, "weight")
+                  seq_starts: torch.Tensor, state_slots: torch.Tensor, weight_t: torch.Tensor | None = None,
+                  bias: torch.Tensor | None = None, residual: bool = True, act: str = "none") -> torch.Tensor:
+    """A causal convolution per channel for a ragged batch, ``weight [width, taps]`` float32 with
+    tap ``taps - 1`` on the token itself: ``x + conv(x)`` (``residual``, the default) or
+    ``act(conv(x) + bias)`` with ``act`` "none" or "silu". ``x [tokens, width]`` may be a column
+    range of a wider matrix (its rows keep their stride). ``state [slots, taps - 1, width]`` (type
+    of ``x``) holds every request's last inputs and is brought up to date. ``weight_t`` (the
+    weights as ``[taps, width]``) lets bfloat16 rows of a width that is a multiple of 8 take the
+    16-byte kernel."""
+    if not x.is_cuda or x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be a CUDA matrix whose rows are contiguous")
+    _need(weight, torch.float32, "weight")
     if weight_t is not None:
         _need(weight_t, torch.float32, "weight_t")
         if weight_t.shape != (weight.shape[1], weight.shape[0]):
@@ -123,6 +172,10 @@ def conv_residual(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | N
     taps = weight.shape[1]
     if weight.shape[0] != width:
         raise ValueError("conv weight does not fit the width")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != width:
+            raise ValueError("conv bias does not fit the width")
     if taps > 1:
         _need(state, x.dtype, "state")
         if state.shape[1:] != (taps - 1, width):
@@ -130,10 +183,11 @@ def conv_residual(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | N
     seqs = seq_starts.numel() - 1
     out = _empty((tokens, width), x.dtype, x.device)
     fn = _fn("conv_state", "pkv_conv_residual",
-             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-              c_void_p])
-    _check(fn(_ptr(x), dtype_code(x.dtype), _ptr(weight), _ptr(weight_t), _ptr(state), _ptr(token_seq), _ptr(seq_starts), _ptr(state_slots),
-              _ptr(out), tokens, seqs, width, taps, _stream()), "conv_residual")
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+              c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), dtype_code(x.dtype), x.stride(0) if tokens > 1 else max(x.stride(0), width), _ptr(weight), _ptr(weight_t),
+              _ptr(bias), _ptr(state), _ptr(token_seq), _ptr(seq_starts), _ptr(state_slots), _ptr(out), tokens, seqs, width,
+              taps, int(bool(residual)), {"none": 0, "silu": 1}[act], _stream()), "conv_residual")
     ops.LAUNCHES["count"] += 1 if taps > 1 else 0
     return out
 
@@ -323,4 +377,119 @@ def token_side(hidden: torch.Tensor, delta: torch.Tensor | None, bias: torch.Ten
               _ptr(proj_w), _ptr(table), dtype_code(gate_w.dtype), table.shape[1], table.shape[0], _ptr(ids), int(col0),
               _ptr(norm_w), float(eps), _ptr(out), tokens, width, dim, ACTIVATIONS[act], _ptr(fed_back), _ptr(fed_back_at),
               _ptr(status), _stream()), "token_side")
+    return out
+
+
+def selective_scan(x: torch.Tensor, z: torch.Tensor, dt_pre: torch.Tensor, dt_bias: torch.Tensor, bc: torch.Tensor, b_at: int,
+                   c_at: int, a: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, seq_starts: torch.Tensor,
+                   state_slots: torch.Tensor) -> torch.Tensor:
+    """The selective scan of a Mamba mixer over a ragged batch. ``x`` and ``z`` ``[tokens, inner]``
+    in the compute type (column ranges of wider matrices are fine); ``dt_pre`` float32 ``[tokens,
+    inner]`` (the step sizes before bias and softplus); ``bc`` float32 ``[tokens, ld]`` with
+    ``B`` at column ``b_at`` and ``C`` at ``c_at``; ``a [inner, state]``, ``dt_bias`` and
+    ``d_skip [inner]`` float32; ``state`` float32 ``[slots, inner, state]`` is read and brought up
+    to date. Returns ``y * silu(z)`` ``[tokens, inner]`` in the type of ``x``."""
+    for name, t in (("dt_pre", dt_pre), ("bc", bc)):
+        if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise ValueError(f"{name} must be a float32 CUDA matrix whose rows are contiguous")
+    for name, t in (("x", x), ("z", z)):
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != x.dtype:
+            raise ValueError(f"{name} must be a CUDA matrix whose rows are contiguous")
+    for name, t in (("a", a), ("dt_bias", dt_bias), ("d_skip", d_skip), ("state", state)):
+        _need(t, torch.float32, name)
+    tokens, inner = x.shape
+    n_state = a.shape[1]
+    if a.shape != (inner, n_state) or z.shape != x.shape or dt_pre.shape[0] != tokens or dt_pre.shape[1] < inner or \
+            dt_bias.numel() != inner or d_skip.numel() != inner or state.shape[1:] != (inner, n_state) or bc.shape[0] != tokens:
+        raise ValueError("selective_scan: sizes do not fit")
+    seqs = seq_starts.numel() - 1
+    out = _empty((tokens, inner), x.dtype, x.device)
+
+    def ld(t: torch.Tensor) -> int:
+        return max(t.stride(0), t.shape[1])
+
+    fn = _fn("selective_scan", "pkv_selective_scan",
+             [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), ld(x), _ptr(z), ld(z), dtype_code(x.dtype), _ptr(dt_pre), ld(dt_pre), _ptr(dt_bias), _ptr(bc), ld(bc),
+              int(b_at), int(c_at), _ptr(a), _ptr(d_skip), _ptr(state), _ptr(seq_starts), _ptr(state_slots), _ptr(out), tokens,
+              seqs, inner, n_state, _stream()), "selective_scan")
+    return out
+
+
+def qkv_prepare(qkv: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor | None, rot_dims: int, rot_factor: float,
+                eps: float, unit_norm: bool, k_pool: torch.Tensor, v_pool: torch.Tensor, slots: torch.Tensor | None,
+                n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int, status: torch.Tensor,
+                v_other: torch.Tensor | None = None, blend: torch.Tensor | None = None,
+                keep_values: torch.Tensor | None = None) -> None:
+    """In ``qkv [tokens, >= H dim + G dim + G vdim]`` (columns ``[Q | K | V]``): rotate the first
+    ``rot_dims`` coordinates of every query and key head (``freq [rot_dims / 2]`` float32 angular
+    frequencies, cos and sin times ``rot_factor``), divide those heads by their root mean square
+    (``unit_norm``), write the queries back in place and the keys into ``k_pool [pages, G,
+    page_size, dim]`` at ``slots``; blend the values with ``v_other [tokens, G vdim]`` (weight
+    ``blend``, a float32 tensor of one element: ``(1 - blend) v + blend v_other``) and write them
+    into ``v_pool [pages, G, page_size, vdim]``. ``keep_values [tokens, G vdim]`` (type of ``qkv``)
+    also receives the values as they are cached."""
+    _need(qkv, None, "qkv"); _need(positions, torch.int32, "positions"); _need(k_pool, None, "k_pool")
+    _need(v_pool, k_pool.dtype, "v_pool")
+    tokens, ld = qkv.shape
+    if rot_dims:
+        _need(freq, torch.float32, "freq")
+        if freq.numel() != rot_dims // 2:
+            raise ValueError("freq needs one element per rotated pair")
+    ld_other = 0
+    if v_other is not None:
+        if v_other.dtype != qkv.dtype or v_other.dim() != 2 or v_other.stride(1) != 1 or v_other.shape != (tokens, n_kv * vdim):
+            raise ValueError("v_other must be [tokens, G * vdim] in the type of qkv")
+        _need(blend, torch.float32, "blend")
+        ld_other = v_other.stride(0) if tokens > 1 else n_kv * vdim
+    if k_pool.shape[-3:] != (n_kv, page_size, dim) or v_pool.shape[-3:] != (n_kv, page_size, vdim):
+        raise ValueError("the pools do not fit heads, page size and head sizes")
+    kept = keep_values
+    if kept is not None:
+        _need(kept, qkv.dtype, "keep_values")
+        if kept.shape != (tokens, n_kv * vdim):
+            raise ValueError("keep_values must be [tokens, G * vdim]")
+    pool_slots = k_pool.numel() // (n_kv * dim)
+    fn = _fn("attention_sink", "pkv_qkv_prepare",
+             [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(qkv), dtype_code(qkv.dtype), ld, _ptr(positions), _ptr(freq), int(rot_dims), float(rot_factor), float(eps),
+              int(bool(unit_norm)), _ptr(v_other), ld_other, _ptr(blend), _ptr(kept), _ptr(k_pool), _ptr(v_pool),
+              dtype_code(k_pool.dtype), _ptr(slots), pool_slots, tokens, n_heads, n_kv, dim, vdim, page_size, _ptr(status),
+              _stream()), "qkv_prepare")
+
+
+def attention_sink_rows_per_block() -> int:
+    fn = ops.library("attention_sink").pkv_attention_sink_rows_per_block
+    fn.restype = c_int
+    return int(fn())
+
+
+def attention_sink(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                   seq_starts: torch.Tensor, first_pos: torch.Tensor, work_seq: torch.Tensor, work_row0: torch.Tensor,
+                   n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int, window: int, keep_first: int, scale: float,
+                   softcap: float, status: torch.Tensor) -> torch.Tensor:
+    """Paged causal attention in float32 arithmetic: scores ``q.k * scale``, capped as ``softcap *
+    tanh(score / softcap)`` (0: no cap); query position ``i`` sees key ``j <= i`` when ``i - j <
+    window`` or ``j < keep_first`` (``window`` 0: every earlier key). Query head ``h`` of token
+    ``t`` is ``q[t, h * dim : (h + 1) * dim]`` (``q`` may have further columns). Returns ``[tokens, H
+    * vdim]`` in the type of ``q``. The work list is in blocks of ``attention_sink_rows_per_block()``
+    rows per (entry, key/value head)."""
+    _need(q, None, "q"); _need(k_pool, None, "k_pool"); _need(v_pool, k_pool.dtype, "v_pool")
+    for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
+                    ("work_seq", work_seq), ("work_row0", work_row0)):
+        _need(t, torch.int32, name)
+    tokens = q.shape[0]
+    if q.shape[1] < n_heads * dim:
+        raise ValueError("q is narrower than its heads")
+    out = _empty((tokens, n_heads * vdim), q.dtype, q.device)
+    num_pages = k_pool.numel() // (n_kv * page_size * dim)
+    fn = _fn("attention_sink", "pkv_attention_sink",
+             [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(q), q.shape[1], _ptr(out), dtype_code(q.dtype), _ptr(k_pool), _ptr(v_pool), dtype_code(k_pool.dtype),
+              _ptr(block_table), block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), _ptr(work_row0),
+              work_seq.numel(), n_heads, n_kv, dim, vdim, page_size, int(window), int(keep_first), float(scale), float(softcap),
+              num_pages, _ptr(status), _stream()), "attention_sink")
     return out

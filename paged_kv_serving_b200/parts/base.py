@@ -46,6 +46,11 @@ class PagedKVRequest:
     #: False for a mixer that caches one vector per position and reads its values out of it
     #: (a latent): the group then has no value pool, and ``GroupView.v_pool`` is ``None``.
     values: bool = True
+    #: Size of a value head when it differs from that of a key head (``None``: the same).
+    value_dim: int | None = None
+    #: With a window: the first ``keep_first`` positions of a sequence stay readable for every
+    #: later query, so their pages are never given back while the request lives.
+    keep_first: int = 0
 
 
 @dataclass(frozen=True, slots=True)

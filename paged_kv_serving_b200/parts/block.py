@@ -8,7 +8,7 @@ from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.parts.base import Block, CacheBinding, Normed, Part, StepContext
 
-__all__ = ["ConvSideBlock", "PreNormBlock"]
+__all__ = ["ConvSideBlock", "PostNormBlock", "PreNormBlock"]
 
 
 @register_part("block", "prenorm_residual")
@@ -161,3 +161,70 @@ class ConvSideBlock(Block):
         if self.side is not None:
             update = self.side.forward(hidden, update, ctx, bias)
         return update
+
+
+@register_part("block", "postnorm_residual")
+class PostNormBlock(Block):
+    """Residual arrangement with the norm on each sublayer's output: ``x += norm1(mixer(x))``, then
+    (with a feed-forward) ``x += norm2(feed_forward(x))``. The sublayers read the stream itself, in
+    the compute type.
+
+    The hand-over between blocks uses ``Block``'s interface with an ``IdentityNorm`` as this
+    block's first norm: what a block before may leave behind is the stream in the compute type.
+    This block adds its updates itself (the kernel that normalises an update also adds it and
+    writes the copy of the stream the next sublayer reads), so it hands on a ``Normed`` for a
+    block of its own kind that follows and ``None`` (nothing pending) otherwise.
+    """
+
+    def __init__(self, mixer_norm: Part, mixer: Part, ff_norm: Part | None = None, feed_forward: Part | None = None) -> None:
+        from paged_kv_serving_b200.parts.norms import IdentityNorm
+
+        if (ff_norm is None) != (feed_forward is None):
+            raise ValueError("a feed-forward and its norm go together")
+        self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward = mixer_norm, mixer, ff_norm, feed_forward
+        self.reads = IdentityNorm()
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(child.graph_safe for child in self.sub_parts().values())
+
+    def sub_parts(self) -> dict[str, Part]:
+        parts = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ff_norm": self.ff_norm, "feed_forward": self.feed_forward}
+        return {name: part for name, part in parts.items() if part is not None}
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def state_requests(self):
+        return self.mixer.state_requests()
+
+    def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
+        for child in self.sub_parts().values():
+            if type(child).plan_step is not Part.plan_step:
+                child.plan_step(ctx, binding)
+
+    @property
+    def first_norm(self) -> Part:
+        return self.reads
+
+    def forward(self, hidden: torch.Tensor, pending: "torch.Tensor | Normed | None", ctx: StepContext,
+                binding: CacheBinding | None, next_norm: Part | None = None) -> "Normed | None":
+        from paged_kv_serving_b200.parts.norms import IdentityNorm
+
+        if isinstance(pending, Normed):
+            if pending.norm is not self.reads:
+                raise ValueError("the stream was normalised for another block than the one that runs next")
+            x = gemm.as_tensor(pending.values)
+        else:
+            x = self.reads.add_norm(hidden, pending, ctx.dtype)
+        copy_type = None if ctx.dtype == torch.float32 else ctx.dtype      # in float32 the stream is its own copy
+        wants_copy = isinstance(next_norm, IdentityNorm)
+        update = self.mixer.forward(x, ctx, binding)
+        last = self.feed_forward is None
+        x = self.mixer_norm.norm_add(hidden, update, copy_type if (not last or wants_copy) else None)
+        if not last:
+            update = self.feed_forward.forward(hidden if x is None else x, ctx)
+            x = self.ff_norm.norm_add(hidden, update, copy_type if wants_copy else None)
+        if wants_copy:
+            return Normed(hidden if x is None else x, next_norm)
+        return None

@@ -9,7 +9,7 @@ from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.parts.base import ParamSpec, Part, StepContext
 
-__all__ = ["BiasedDense", "RoutedExperts", "SwiGLU"]
+__all__ = ["BiasedDense", "GatedRoutedExperts", "RoutedExperts", "SwiGLU"]
 
 
 @register_part("feed_forward", "swiglu")
@@ -165,3 +165,71 @@ class RoutedExperts(Part):
         gate = logits[:, self.experts] if self.shared_inner else None
         inner = mixer_ops.expert_act(up, weights, gate, self.experts, self.inner, self.shared_inner, self.activation)
         return gemm.linear(inner, self.down)
+
+
+@register_part("feed_forward", "gated_routed_experts")
+class GatedRoutedExperts(Part):
+    """A mixture of small gated experts ``W_down (act(W_gate x) * (W_up x))`` without biases
+    (``act`` SiLU by default). Router logits ``W_router x + b_router`` are float32; a token uses
+    the ``top`` experts with the largest logits, weighted by the softmax over those logits only
+    (``renormalise``; otherwise by their softmax scores over all experts). An optional shared
+    expert of the same form runs for every token and is added with weight 1.
+
+    Kernels, as in ``RoutedExperts``: one product over the stacked gate and up projections of all
+    experts (and the shared one), the gated activation scaled by the router's weight of each
+    column's expert (exact zeros for an expert the token does not use), one product over the
+    stacked down-projections, whose result stays float32. Nothing depends on values read back to
+    the host, so decode steps can be captured.
+    """
+
+    graph_safe = True
+
+    def __init__(self, width: int, experts: int, top: int, inner: int, shared_inner: int = 0, activation: str = "silu",
+                 router_bias: bool = True, renormalise: bool = True) -> None:
+        if not 1 <= top <= experts:
+            raise ValueError("top must be between 1 and the number of experts")
+        self.width, self.experts, self.top, self.inner = int(width), int(experts), int(top), int(inner)
+        self.shared_inner, self.activation = int(shared_inner), activation
+        self.router_bias, self.renormalise = bool(router_bias), bool(renormalise)
+        self.columns = self.experts * self.inner + self.shared_inner
+        self.up_at = -(-self.columns // 8) * 8           # the up columns start on a 16-byte boundary
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        specs = {"router": ParamSpec((self.experts, self.width))}
+        if self.router_bias:
+            specs["router_b"] = ParamSpec((self.experts,), "vector")
+        names = [f"e{e}" for e in range(self.experts)]
+        for name in names:
+            specs[f"{name}_gate"] = ParamSpec((self.inner, self.width))
+            specs[f"{name}_up"] = ParamSpec((self.inner, self.width))
+            specs[f"{name}_down"] = ParamSpec((self.width, self.inner))
+        if self.shared_inner:
+            specs["shared_gate"] = ParamSpec((self.shared_inner, self.width))
+            specs["shared_up"] = ParamSpec((self.shared_inner, self.width))
+            specs["shared_down"] = ParamSpec((self.width, self.shared_inner))
+        return specs
+
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        names = [f"e{e}" for e in range(self.experts)] + (["shared"] if self.shared_inner else [])
+        first = params["router"]
+        gate_up = torch.zeros((2 * self.up_at, self.width), dtype=first.dtype, device=first.device)
+        gate_up[:self.columns] = torch.cat([params[f"{n}_gate"] for n in names], dim=0)
+        gate_up[self.up_at:self.up_at + self.columns] = torch.cat([params[f"{n}_up"] for n in names], dim=0)
+        self.gate_up = gate_up                                              # [gates (padded) | ups (padded), width]
+        self.down = torch.cat([params[f"{n}_down"] for n in names], dim=1).contiguous()     # [width, columns]
+        rows = -(-self.experts // 8) * 8
+        router = torch.zeros((rows, self.width), dtype=first.dtype, device=first.device)
+        router[:self.experts] = first
+        self.router = router
+        self.router_b = params["router_b"].contiguous() if self.router_bias else None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        from paged_kv_serving_b200.ops import mixer_ops
+
+        logits = gemm.linear(x, self.router, out_dtype=torch.float32)       # [tokens, experts (padded)]
+        weights = mixer_ops.route_top(logits, self.experts, self.top, bias=self.router_b, renormalise=self.renormalise)
+        gate_up = gemm.linear(x, self.gate_up)
+        inner = mixer_ops.expert_gated_act(gate_up, self.up_at, weights, self.experts, self.inner, self.shared_inner,
+                                           self.activation)
+        # the float32 result of the last product goes to a norm
+        return gemm.linear(inner, self.down, out_dtype=torch.float32)

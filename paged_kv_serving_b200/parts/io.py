@@ -14,17 +14,18 @@ __all__ = ["LinearHead", "TokenEmbedding"]
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
-    """``hidden = table[ids]`` widened to float32
+    """``hidden = table[ids] * scale`` widened to float32, ``scale`` 1 unless given
     (reference: src/paged_kv_serving/engine/model.py:266-267). ``forward(ctx)`` reads the step's
     token ids from ``ctx`` (and, for a token that was sampled on the device by the step before,
-    from ``ctx.fed_back_ids``). An architecture whose embeddings are scaled, summed with others
-    or looked up otherwise gives its layout another part with the same ``forward``."""
+    from ``ctx.fed_back_ids``). An architecture whose embeddings are summed with others or
+    looked up otherwise gives its layout another part with the same ``forward``."""
 
     graph_safe = True
 
-    def __init__(self, vocab_size: int, width: int) -> None:
+    def __init__(self, vocab_size: int, width: int, scale: float = 1.0) -> None:
         self.vocab_size = int(vocab_size)
         self.width = int(width)
+        self.scale = float(scale)
         self.table: torch.Tensor | None = None
 
     def param_specs(self) -> dict[str, ParamSpec]:
@@ -35,7 +36,7 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         fed_back_at = ctx.ints(ctx.TOKEN_FEEDBACK) if ctx.fed_back_ids is not None else None
-        return ops.embedding_gather(self.table, ctx.ints(ctx.TOKEN_IDS), ctx.status, ctx.fed_back_ids, fed_back_at)
+        return ops.embedding_gather(self.table, ctx.ints(ctx.TOKEN_IDS), ctx.status, ctx.fed_back_ids, fed_back_at, self.scale)
 
 
 @register_part("head", "linear")

@@ -9,7 +9,7 @@ from paged_kv_serving_b200.ops import gemm
 from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.parts.base import ParamSpec, Part
 
-__all__ = ["RMSNorm", "ScalarRMSNorm"]
+__all__ = ["IdentityNorm", "OffsetRMSNorm", "RMSNorm", "ScalarRMSNorm"]
 
 
 @register_part("norm", "rmsnorm")
@@ -42,6 +42,14 @@ class RMSNorm(Part):
         the result, where the kernels can do that. ``chain`` as in ``ops.gemm.linear``."""
         return gemm.linear_add_norm(x, w_nk, hidden, self.weight, self.eps, out_dtype, chain=chain)
 
+    def norm_add(self, hidden: torch.Tensor, update: torch.Tensor, out_dtype: torch.dtype | None = None
+                 ) -> torch.Tensor | None:
+        """The norm on a sublayer's output: ``hidden += norm(update)`` in place, and, with
+        ``out_dtype``, the updated stream in that type (for a sublayer that reads the stream itself)."""
+        from paged_kv_serving_b200.ops import mixer_ops
+
+        return mixer_ops.norm_residual(hidden, update, self.weight, self.eps, out_dtype)
+
 
 @register_part("norm", "scalar_rmsnorm")
 class ScalarRMSNorm(RMSNorm):
@@ -54,3 +62,37 @@ class ScalarRMSNorm(RMSNorm):
 
     def load(self, params: dict[str, torch.Tensor]) -> None:
         self.weight = params["weight"].reshape(1).expand(self.width).contiguous()
+
+
+@register_part("norm", "offset_rmsnorm")
+class OffsetRMSNorm(RMSNorm):
+    """RMS norm whose stored weight is centred on zero: ``y = x / sqrt(mean(x^2) + eps) * (offset +
+    w)`` with ``offset`` 1 unless given. The sum is formed once at load (in float32), after which
+    the kernels of ``RMSNorm`` serve it unchanged."""
+
+    def __init__(self, width: int, eps: float, offset: float = 1.0) -> None:
+        super().__init__(width, eps)
+        self.offset = float(offset)
+
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        self.weight = (params["weight"].to(torch.float32) + self.offset).contiguous()
+
+
+@register_part("norm", "identity")
+class IdentityNorm(Part):
+    """No norm at all, in the shape of one: ``add_norm`` adds the pending update to the stream and
+    hands out the stream itself in the asked type. It is the ``first_norm`` of a block whose
+    sublayers read the stream as it is, so that the block before can leave that copy behind."""
+
+    graph_safe = True
+
+    def add_norm(self, hidden: torch.Tensor, delta: torch.Tensor | None, out_dtype: torch.dtype,
+                 rows: torch.Tensor | None = None) -> torch.Tensor:
+        from paged_kv_serving_b200.ops import mixer_ops
+
+        if rows is not None:
+            raise ValueError("the identity norm hands out whole streams only")
+        if delta is None and out_dtype == torch.float32:
+            return hidden
+        out = mixer_ops.residual_add(hidden, delta, None, None if out_dtype == torch.float32 else out_dtype)
+        return hidden if out is None else out

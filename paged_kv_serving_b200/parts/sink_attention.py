@@ -1,0 +1,144 @@
+"""Attention over a sliding window that also keeps the first tokens, with capped scores."""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from paged_kv_serving_b200.config.registry import register_part
+from paged_kv_serving_b200.ops import arena, gemm, mixer_ops
+from paged_kv_serving_b200.parts.base import CacheBinding, PagedKVRequest, ParamSpec, Part, StepContext
+from paged_kv_serving_b200.parts.position import ScaledRotaryFrequencies
+
+__all__ = ["SinkWindowAttention"]
+
+
+def _round_up(value: int, multiple: int) -> int:
+    return -(-value // multiple) * multiple
+
+
+@register_part("mixer", "sink_window_attention")
+class SinkWindowAttention(Part):
+    """Causal grouped-query softmax attention with these ingredients, each a parameter:
+
+    * ``H`` query heads and ``G`` key/value heads (query head ``h`` reads key/value head ``h // (H
+      // G)``), keys and queries of size ``dim``, values of size ``vdim``; ``q = W_q x``, ``k = W_k
+      x``, ``v = W_v x`` without biases, ``W_o`` on the concatenated heads;
+    * ``rotary``: a ``ScaledRotaryFrequencies`` that turns the first coordinates of every query and
+      key head by the token's position (``None``: no rotation);
+    * ``unit_norm``: after the rotation every query and key head is divided by its root mean square
+      (``eps`` inside the root), no weight;
+    * ``score = q . k * scale``, then, with ``softcap`` ``c > 0``, ``c * tanh(score / c)``;
+    * ``window`` and ``keep_first``: position ``i`` sees ``j <= i`` when ``i - j < window`` or ``j <
+      keep_first`` (``window=None``: all earlier positions); kept tokens keep their own positions;
+    * ``value_share``: ``"source"`` leaves this layer's values of the step's tokens in the step's
+      scratch under ``share_key``; ``"blend"`` replaces ``v`` by ``(1 - lambda) v + lambda v_source``
+      with ``lambda`` the tensor ``vmix`` and ``v_source`` what the source layer left for the same
+      tokens; the blended values are what is cached. ``None``: plain values.
+
+    Keys are cached rotated and normalised, in pages of ``[G, page_size, dim]`` and ``[G,
+    page_size, vdim]``. Angles, norms, scores, softmax and the blend are float32 arithmetic.
+    """
+
+    graph_safe = True
+
+    def __init__(self, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
+                 rotary: ScaledRotaryFrequencies | None = None, unit_norm: bool = True, eps: float = 1e-6,
+                 softcap: float = 0.0, window: int | None = None, keep_first: int = 0, value_share: str | None = None,
+                 share_key: str = "sink_attention/shared_values") -> None:
+        if n_heads < 1 or n_kv_heads < 1 or n_heads % n_kv_heads:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if window is not None and window < 1:
+            raise ValueError("window must be >= 1 or None")
+        if keep_first < 0 or softcap < 0:
+            raise ValueError("keep_first and softcap must be >= 0")
+        if value_share not in (None, "source", "blend"):
+            raise ValueError("value_share is None, 'source' or 'blend'")
+        if rotary is not None and rotary.dims > dim:
+            raise ValueError("more rotated coordinates than a head has")
+        self.width, self.n_heads, self.n_kv_heads = int(width), int(n_heads), int(n_kv_heads)
+        self.dim, self.vdim = int(dim), int(vdim)
+        self.scale, self.softcap, self.eps = float(scale), float(softcap), float(eps)
+        self.rotary, self.unit_norm = rotary, bool(unit_norm)
+        self.window, self.keep_first = window, int(keep_first)
+        self.value_share, self.share_key = value_share, share_key
+        self.q_cols = self.n_heads * self.dim
+        self.kv_cols = self.n_kv_heads * (self.dim + self.vdim)
+        self.fused_rows = _round_up(self.q_cols + self.kv_cols, 8)
+
+    @property
+    def group_size(self) -> int:
+        return self.n_heads // self.n_kv_heads
+
+    def param_specs(self) -> dict[str, ParamSpec]:
+        specs = {
+            "q": ParamSpec((self.q_cols, self.width)), "k": ParamSpec((self.n_kv_heads * self.dim, self.width)),
+            "v": ParamSpec((self.n_kv_heads * self.vdim, self.width)), "o": ParamSpec((self.width, self.n_heads * self.vdim)),
+        }
+        if self.value_share is not None:
+            specs["vmix"] = ParamSpec((), "vector")
+        return specs
+
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        q = params["q"]
+        fused = torch.zeros((self.fused_rows, self.width), dtype=q.dtype, device=q.device)
+        at = 0
+        for name in ("q", "k", "v"):
+            rows = params[name].shape[0]
+            fused[at:at + rows] = params[name]
+            at += rows
+        self.qkv = fused                                   # [H dim + G dim + G vdim (padded), width]
+        self.o = params["o"].contiguous()
+        self.blend = params["vmix"].reshape(1).contiguous() if "vmix" in params else None
+
+    def cache_request(self) -> PagedKVRequest:
+        return PagedKVRequest(self.n_kv_heads, self.dim, self.window, value_dim=self.vdim,
+                              keep_first=self.keep_first if self.window is not None else 0)
+
+    # --- per step ------------------------------------------------------------------------
+
+    def _work_names(self) -> tuple[str, str]:
+        return (f"sink_attention/work_seq/g{self.group_size}", f"sink_attention/work_row0/g{self.group_size}")
+
+    def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
+        seq_name, row_name = self._work_names()
+        if seq_name in ctx.arena:
+            return
+        rows_per_block = mixer_ops.attention_sink_rows_per_block()
+        rows = np.asarray(ctx.seq_lens, dtype=np.int64) * self.group_size
+        blocks = (rows + rows_per_block - 1) // rows_per_block
+        work_seq = np.repeat(np.arange(len(rows), dtype=np.int64), blocks)
+        starts = np.cumsum(blocks) - blocks
+        work_row0 = (np.arange(int(blocks.sum()), dtype=np.int64) - np.repeat(starts, blocks)) * rows_per_block
+        ctx.arena.add(seq_name, work_seq)
+        ctx.arena.add(row_name, work_row0)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding) -> torch.Tensor:
+        group = ctx.groups[binding.group]
+        k_pool, v_pool = group.k_pool[binding.index], group.v_pool[binding.index]
+        slots = ctx.ints(group.slots_name) if binding.write else None
+        qkv = gemm.linear(x, self.qkv)
+        other = None
+        if self.value_share == "blend":
+            other = ctx.scratch.get(self.share_key)
+            if other is None:
+                raise RuntimeError("a layer blends its values with those of a layer that has not run in this step")
+        shared = None
+        if self.value_share == "source":
+            # the values of the step's tokens as this layer caches them, for the layers that blend with
+            # them: a copy that lives as long as the step
+            shared = arena.empty_for_step((qkv.shape[0], self.n_kv_heads * self.vdim), qkv.dtype, qkv.device)
+            ctx.scratch[self.share_key] = shared
+        rotary = self.rotary if self.rotary is not None and self.rotary.dims else None
+        mixer_ops.qkv_prepare(
+            qkv, ctx.ints(ctx.POSITIONS), rotary.device_frequencies(ctx.device) if rotary else None,
+            rotary.dims if rotary else 0, rotary.amplitude if rotary else 1.0, self.eps, self.unit_norm, k_pool, v_pool,
+            slots, self.n_heads, self.n_kv_heads, self.dim, self.vdim, group.page_size, ctx.status,
+            v_other=other, blend=self.blend if other is not None else None, keep_values=shared)
+        seq_name, row_name = self._work_names()
+        attended = mixer_ops.attention_sink(
+            qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
+            ctx.ints(seq_name), ctx.ints(row_name), self.n_heads, self.n_kv_heads, self.dim, self.vdim, group.page_size,
+            self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status)
+        # the float32 result of the last product goes to a norm
+        return gemm.linear(attended, self.o, out_dtype=torch.float32)
