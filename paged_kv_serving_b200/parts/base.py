@@ -25,10 +25,13 @@ __all__ = [
 class ParamSpec:
     """Shape and role of one tensor. ``matrix``: an operand of a matrix product, held in the
     engine's compute type; ``vector``: an element-wise parameter, held in float32;
-    ``int_table``: an integer table, held in int32."""
+    ``int_table``: an integer table, held in int32. ``init`` is a hint for the random-weights
+    mode only: ``(mean, spread)`` of a vector's values where ones would make a poor model (a
+    weight stored around zero, a decay's logarithm, a bias)."""
 
     shape: tuple[int, ...]
     kind: str = "matrix"
+    init: tuple[float, float] | None = None
 
     def __post_init__(self) -> None:
         if self.kind not in ("matrix", "vector", "int_table"):

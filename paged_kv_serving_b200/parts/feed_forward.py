@@ -197,7 +197,7 @@ class GatedRoutedExperts(Part):
     def param_specs(self) -> dict[str, ParamSpec]:
         specs = {"router": ParamSpec((self.experts, self.width))}
         if self.router_bias:
-            specs["router_b"] = ParamSpec((self.experts,), "vector")
+            specs["router_b"] = ParamSpec((self.experts,), "vector", init=(0.0, 0.1))
         names = [f"e{e}" for e in range(self.experts)]
         for name in names:
             specs[f"{name}_gate"] = ParamSpec((self.inner, self.width))

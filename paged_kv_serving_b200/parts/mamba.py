@@ -52,10 +52,12 @@ class Mamba1(Part):
     def param_specs(self) -> dict[str, ParamSpec]:
         return {
             "in_proj": ParamSpec((2 * self.inner, self.width)),
-            "conv": ParamSpec((self.inner, self.taps), "vector"), "conv_b": ParamSpec((self.inner,), "vector"),
+            "conv": ParamSpec((self.inner, self.taps), "vector", init=(0.0, 0.4)),
+            "conv_b": ParamSpec((self.inner,), "vector", init=(0.0, 0.1)),
             "x_proj": ParamSpec((self.dt_rank + 2 * self.state, self.inner)),
-            "dt_proj": ParamSpec((self.inner, self.dt_rank)), "dt_b": ParamSpec((self.inner,), "vector"),
-            "A_log": ParamSpec((self.inner, self.state), "vector"), "D": ParamSpec((self.inner,), "vector"),
+            "dt_proj": ParamSpec((self.inner, self.dt_rank)), "dt_b": ParamSpec((self.inner,), "vector", init=(-2.0, 0.5)),
+            "A_log": ParamSpec((self.inner, self.state), "vector", init=(0.0, 0.5)),
+            "D": ParamSpec((self.inner,), "vector", init=(1.0, 0.1)),
             "o": ParamSpec((self.width, self.inner)),
         }
 

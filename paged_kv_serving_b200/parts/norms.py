@@ -74,6 +74,9 @@ class OffsetRMSNorm(RMSNorm):
         super().__init__(width, eps)
         self.offset = float(offset)
 
+    def param_specs(self) -> dict[str, ParamSpec]:
+        return {"weight": ParamSpec((self.width,), "vector", init=(1.0 - self.offset, 0.0))}
+
     def load(self, params: dict[str, torch.Tensor]) -> None:
         self.weight = (params["weight"].to(torch.float32) + self.offset).contiguous()
 

@@ -76,7 +76,7 @@ class SinkWindowAttention(Part):
             "v": ParamSpec((self.n_kv_heads * self.vdim, self.width)), "o": ParamSpec((self.width, self.n_heads * self.vdim)),
         }
         if self.value_share is not None:
-            specs["vmix"] = ParamSpec((), "vector")
+            specs["vmix"] = ParamSpec((), "vector", init=(0.5, 0.0))
         return specs
 
     def load(self, params: dict[str, torch.Tensor]) -> None:

@@ -1,7 +1,7 @@
 """The random-weights mode: tensors from a configuration and a seed, and model folders of them.
 
-Matrices are drawn from ``N(0, std)`` and norm weights are ones (plus an optional jitter, for
-tests that must notice a wrong norm weight). Two generators exist and are documented apart:
+Matrices are drawn from ``N(0, std)`` and vectors are ones, or what their ``ParamSpec.init``
+says (plus an optional jitter, for tests that must notice a wrong norm weight). Two generators exist and are documented apart:
 ``random_tensors`` draws on the host with NumPy's PCG64 in sorted tensor-name order and is what
 model folders are written from, so that any other program can draw the same arrays;
 ``random_tensors_on_device`` draws with torch's device generator for shapes too large to pass
@@ -38,7 +38,8 @@ def random_tensors(specs: dict[str, ParamSpec], seed: int, std: float | Callable
             out[name] = torch.zeros(spec.shape, dtype=torch.int32)
         elif spec.kind == "vector":
             # (np.asarray: a tensor without axes, one number, comes back from the generator as a scalar)
-            values = np.asarray(1.0 + norm_jitter * rng.standard_normal(spec.shape), dtype=np.float32)
+            mean, spread = spec.init if spec.init is not None else (1.0, 0.0)
+            values = np.asarray(mean + (spread + norm_jitter) * rng.standard_normal(spec.shape), dtype=np.float32)
             out[name] = torch.from_numpy(values.copy())
         else:
             scale = std(name) if callable(std) else std
@@ -57,7 +58,10 @@ def random_tensors_on_device(specs: dict[str, ParamSpec], seed: int, std: float,
         if spec.kind == "int_table":
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
         elif spec.kind == "vector":
-            out[name] = torch.ones(spec.shape, dtype=torch.float32, device=device)
+            mean, spread = spec.init if spec.init is not None else (1.0, 0.0)
+            out[name] = torch.full(spec.shape, float(mean), dtype=torch.float32, device=device)
+            if spread:
+                out[name] += spread * torch.randn(spec.shape, dtype=torch.float32, device=device, generator=generator)
         else:
             rows = spec.shape[0]
             tensor = torch.empty(spec.shape, dtype=dtype, device=device)
