@@ -382,11 +382,11 @@ SINGLE = {
     "attention_grouped_keys": _single(_attention(6, 2, 8, 4, window=200, keep=0, v_mix=False, rot_dims=4)),
     "attention_partly_rotated_and_stretched": _single(_attention(2, 1, 16, 8, window=200, keep=0, rot_dims=6, base=50.0, v_mix=False)),
     "attention_unrotated": _single(_attention(2, 1, 12, 8, window=200, keep=0, rot_dims=0, scaling=False, v_mix=False)),
-    "attention_tight_cap": _single(_attention(2, 2, 8, 8, window=200, keep=0, softcap=0.5, scale=2.0, v_mix=False)),
-    "attention_window": _single(_attention(2, 2, 8, 8, window=6, keep=0, v_mix=False)),
-    "attention_window_of_one": _single(_attention(2, 2, 8, 8, window=1, keep=0, v_mix=False)),
-    "attention_window_and_kept_tokens": _single(_attention(2, 2, 8, 8, window=6, keep=3, v_mix=False)),
-    "attention_kept_tokens_beyond_a_page": _single(_attention(2, 1, 8, 8, window=5, keep=11, v_mix=False)),
+    "attention_tight_cap": _single(_attention(2, 2, 8, 8, window=200, keep=0, rot_dims=8, softcap=0.5, scale=2.0, v_mix=False)),
+    "attention_window": _single(_attention(2, 2, 8, 8, window=6, keep=0, rot_dims=4, v_mix=False)),
+    "attention_window_of_one": _single(_attention(2, 2, 8, 8, window=1, keep=0, rot_dims=8, v_mix=False)),
+    "attention_window_and_kept_tokens": _single(_attention(2, 2, 8, 8, window=6, keep=3, rot_dims=8, v_mix=False)),
+    "attention_kept_tokens_beyond_a_page": _single(_attention(2, 1, 8, 8, window=5, keep=11, rot_dims=2, v_mix=False)),
     "attention_wide_heads": _single(_attention(1, 1, 160, 72, window=30, keep=2, rot_dims=64)),
     "mamba": _single(_mamba(32, 8, 4, 4)),
     "mamba_one_tap": _single(_mamba(24, 16, 2, 1)),
@@ -417,8 +417,9 @@ def test_each_mechanism_alone(what, dtype):
 def test_value_mixing_takes_the_first_mixing_layers_values_of_the_same_token():
     """Three attention layers of which the second and third mix: with lambda 1 in the third its
     values are the second layer's, with lambda 0 its own; the first layer's values never enter."""
-    layers = [_layer(_attention(2, 2, 8, 8, window=50, keep=0, v_mix=False), None),
-              _layer(_attention(2, 2, 8, 8, window=50, keep=0), None), _layer(_attention(2, 2, 8, 8, window=50, keep=0), None)]
+    layers = [_layer(_attention(2, 2, 8, 8, window=50, keep=0, rot_dims=8, v_mix=False), None),
+              _layer(_attention(2, 2, 8, 8, window=50, keep=0, rot_dims=8), None),
+              _layer(_attention(2, 2, 8, 8, window=50, keep=0, rot_dims=8), None)]
     config = _model(layers, vocab=40, width=32)
     tokens = tokens_for(config, 30, seed=1)
     for lam in (0.0, 1.0, 0.25):
