@@ -490,7 +490,9 @@ def run_reference_workload() -> dict:
 
 
 def run_design(args) -> dict:
-    """``--design revupel``: the design and the Llama-style decoder side by side, per size."""
+    """``--design NAME``: the design and the models it is compared with side by side, per size:
+    Revupel beside the Llama-style decoder; Tiburax beside Revupel (the closest model: attention and
+    a recurrent mixer in turn, routed experts) and the Llama-style decoder."""
     import torch
 
     from paged_kv_serving_b200 import design_bench
@@ -500,15 +502,18 @@ def run_design(args) -> dict:
     clocks = ClockSampler()
     clocks.start()
     sizes = {}
-    for size in [s for s in args.design_sizes.split(",") if s]:
-        sizes[size] = {
-            "revupel": design_bench.measure(design_bench.revupel_config(size), peaks, prefill_tokens=args.prefill_tokens,
-                                            batch=args.batch, context=args.prompt_len, steps=min(args.steps, 32), warmup=args.warmup),
-            "llama_style": design_bench.measure(design_bench.llama_like(size), peaks, prefill_tokens=args.prefill_tokens,
-                                                batch=args.batch, context=args.prompt_len, steps=min(args.steps, 32),
-                                                warmup=args.warmup),
-        }
+    def measured(config):
+        out = design_bench.measure(config, peaks, prefill_tokens=args.prefill_tokens, batch=args.batch, context=args.prompt_len,
+                                   steps=min(args.steps, 32), warmup=args.warmup)
         torch.cuda.empty_cache()
+        return out
+
+    for size in [s for s in args.design_sizes.split(",") if s]:
+        sizes[size] = {}
+        if args.design == "tiburax":
+            sizes[size]["tiburax"] = measured(design_bench.tiburax_config(size))
+        sizes[size]["revupel"] = measured(design_bench.revupel_config(size))
+        sizes[size]["llama_style"] = measured(design_bench.llama_like(size))
     clocks.stop()
     return {"impl": "ours", "design": args.design, "dtype": "bf16", "data": "synthetic: random ids, random N(0, 0.02) weights",
             "peaks": peaks, "sizes": sizes, "clocks": clocks.summary()}
@@ -532,9 +537,9 @@ def main() -> int:
     parser.add_argument("--only-workloads", action="store_true", help="leave out the headline run (for profiling a workload)")
     parser.add_argument("--workload-layers", type=int, default=0, help="fewer layers for those workloads (0: all)")
     parser.add_argument("--serve-requests", type=int, default=256)
-    parser.add_argument("--design", choices=("revupel",), default=None,
+    parser.add_argument("--design", choices=("revupel", "tiburax"), default=None,
                         help="instead of the default run: prefill and decode throughput of this design at layer sizes of "
-                             "real models, beside the Llama-style decoder at equal sizes, with every kernel against its roofline")
+                             "real models, beside the framework's closest models at equal sizes, with every kernel against its roofline")
     parser.add_argument("--design-sizes", default="1b,7b", help="which of the sizes of paged_kv_serving_b200.design_bench")
     args = parser.parse_args()
     if args.impl == "reference":

@@ -52,11 +52,14 @@ struct DecodeState {
 // Folds keys wbase .. wbase + 15 (rows 16 warp .. of the stage at `stage_smem`) into `st`:
 // scores = q.k * scale, keys outside [key_lo, key_hi), after a row's query position or before its
 // window masked, shift = new maximum if finite else 0 (the reference's online softmax,
-// src/paged_kv_serving/engine/attention.py:100-116).
+// src/paged_kv_serving/engine/attention.py:100-116). With a window, keys below position `keep` stay
+// visible; with cap_log2 > 0 the scores are capped, c * tanh(score * scale / c) (cap_log2 = c
+// log2(e), cap_x = 2 scale / c * log2(e); tanh(x) = 1 - 2 / (1 + e^(2x))).
 template <int HD>
 __device__ __forceinline__ void decode_tile(uint8_t* stage_smem, int warp, int lane, const uint32_t (&qa)[HD / 16][4],
                                             DecodeState<HD>& st, int wbase, int key_lo, int key_hi, int qpos_a,
-                                            int qpos_b, int window, float scale_log2) {
+                                            int qpos_b, int window, float scale_log2, int keep = 0, float cap_log2 = 0.0f,
+                                            float cap_x = 0.0f) {
   constexpr int PANELS = HD / 64;
   constexpr uint32_t PANEL_BYTES = DT_BN * 128;
   constexpr uint32_t HALF_BYTES = PANELS * PANEL_BYTES;
@@ -73,7 +76,7 @@ __device__ __forceinline__ void decode_tile(uint8_t* stage_smem, int warp, int l
   const uint32_t v_base = k_base + HALF_BYTES;
   float (&o)[DTILES][4] = st.o;
   float &m_a = st.m_a, &m_b = st.m_b, &l_a = st.l_a, &l_b = st.l_b;
-  if (wbase < key_hi && wbase + 15 >= key_lo) {
+  if (wbase < key_hi && (wbase + 15 >= key_lo || wbase < keep)) {
     if (wbase + 16 > key_hi) {
       // slots of the last page past the last key may hold anything (0 x NaN = NaN): clear the
       // value rows this warp will read
@@ -102,8 +105,10 @@ __device__ __forceinline__ void decode_tile(uint8_t* stage_smem, int warp, int l
       for (int e = 0; e < 4; ++e) {
         const int kpos = wbase + jj * 8 + 2 * t4 + (e & 1);
         const int qpos = (e < 2) ? qpos_a : qpos_b;
-        const bool visible = kpos <= qpos && (window == 0 || kpos > qpos - window);
-        const float v = visible ? sc[jj][e] * scale_log2 : -INFINITY;
+        const bool visible = kpos <= qpos && (window == 0 || kpos > qpos - window || kpos < keep);
+        float scaled = sc[jj][e] * scale_log2;
+        if (cap_log2 > 0.0f) scaled = cap_log2 * (1.0f - 2.0f / (1.0f + exp2f(sc[jj][e] * cap_x)));
+        const float v = visible ? scaled : -INFINITY;
         sc[jj][e] = v;
         if (e < 2) tmax_a = fmaxf(tmax_a, v); else tmax_b = fmaxf(tmax_b, v);
       }

@@ -48,6 +48,8 @@ struct DecTmaParams {
   int pool_rows;
   int* status;
   int landing_floats;           // room behind the ring for the states the other splits push (0: they are fetched)
+  int keep_first;               // with a window: keys below this position stay visible
+  float cap_log2, cap_x;        // score cap (see decode_tile); 0: none
 };
 
 // Pushing a split's state into the first block of its cluster: a store into that block's shared
@@ -95,11 +97,22 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
   const int key_hi = pos0 + n_q;
   const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-  const int tile_first = key_lo / DT_BN, tile_last = (key_hi - 1) / DT_BN;
-  const int tiles_per_split = (tile_last - tile_first + p.num_splits) / p.num_splits;
-  const int tile_begin = tile_first + split * tiles_per_split;
-  const int tile_end = min(tile_last, tile_begin + tiles_per_split - 1);
-  const int n_tiles = max(0, tile_end - tile_begin + 1);
+  // The tiles of an entry as one list: those that hold kept first tokens, then those of the
+  // window (one range where the two meet); the splits share the list.
+  const int keep = p.window > 0 ? min(p.keep_first, key_hi) : 0;
+  int window_tile = key_lo / DT_BN, kept = (keep + DT_BN - 1) / DT_BN;
+  if (kept >= window_tile) {
+    if (kept > 0) window_tile = 0;
+    kept = 0;
+  }
+  const int tile_first = window_tile, kept_tiles = kept, tile_last = (key_hi - 1) / DT_BN;
+  auto tile_of = [=](int at) { return at < kept_tiles ? at : tile_first + (at - kept_tiles); };
+  const int listed = kept_tiles + tile_last - tile_first + 1;
+  const int tiles_per_split = (listed - 1 + p.num_splits) / p.num_splits;
+  const int list_begin = split * tiles_per_split;
+  const int list_end = min(listed - 1, list_begin + tiles_per_split - 1);
+  const int n_tiles = max(0, list_end - list_begin + 1);
+  const int tile_begin = n_tiles ? tile_of(list_begin) : 0, tile_end = n_tiles ? tile_of(list_end) : -1;
   const int32_t* table = p.block_table + (size_t)s * p.table_stride;
 
   if (threadIdx.x == 0) {
@@ -178,9 +191,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       if (has_box) {
-        const int pos = (tile_begin + j) * DT_BN + key_in_tile;
+        const int pos = tile_of(list_begin + j) * DT_BN + key_in_tile;
         int row = p.pool_rows;                                     // outside the pool: zeros
-        if (pos < key_hi && pos + p.page_size > key_lo) {
+        if (pos < key_hi && (pos + p.page_size > key_lo || pos < keep)) {
           const int e = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
           const int page = table_cached ? table_cache[e - entry_first] : table[e];
           row = checked_pool_row(page, p.n_kv, kvh, p.page_size, p.pool_rows, p.status);
@@ -221,9 +234,9 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       const int stage = j % STAGES;
       ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[stage], (j / STAGES) & 1, aborted) ? 1 : 0) != 0;
       if (!ok) break;
-      const int wbase = (tile_begin + j) * DT_BN + warp * 16;
+      const int wbase = tile_of(list_begin + j) * DT_BN + warp * 16;
       decode_tile<HD>(ring + (size_t)stage * STAGE_BYTES, warp, lane, qa, st, wbase, key_lo, key_hi, qpos_a, qpos_b,
-                      p.window, p.scale_log2);
+                      p.window, p.scale_log2, keep, p.cap_log2, p.cap_x);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[stage]);     // this warp is done with the stage
     }
@@ -429,15 +442,18 @@ PKV_EXPORT int pkv_attention_decode_tma_blocks_per_sm(int hd, int deep_ring) {
   return 0;
 }
 
-PKV_EXPORT int pkv_attention_decode_tma(const void* qkv, int q_row_stride, void* out, const void* k_pool,
-                                        const void* v_pool, long long n_pages, const int32_t* block_table,
-                                        int table_stride, const int32_t* seq_starts, const int32_t* first_pos,
-                                        const int32_t* work_seq, int n_work, int max_entry_tokens, int n_heads, int n_kv,
-                                        int hd, int page_size, int window, float scale, int num_splits, int deep_ring,
-                                        int* status, void* stream) {
+// keep_first: with a window, keys below this position stay visible; softcap: scores are capped as
+// softcap * tanh(score * scale / softcap) (0: no cap).
+PKV_EXPORT int pkv_attention_decode_tma_sink(const void* qkv, int q_row_stride, void* out, const void* k_pool,
+                                             const void* v_pool, long long n_pages, const int32_t* block_table,
+                                             int table_stride, const int32_t* seq_starts, const int32_t* first_pos,
+                                             const int32_t* work_seq, int n_work, int max_entry_tokens, int n_heads, int n_kv,
+                                             int hd, int page_size, int window, int keep_first, float scale, float softcap,
+                                             int num_splits, int deep_ring, int* status, void* stream) {
   if (n_work <= 0) return 0;
   if (!pkv_attention_decode_tma_supports(hd, page_size, q_row_stride)) return PKV_ERR_LIMIT;
-  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || window < 0) return PKV_ERR_SIZE;
+  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || window < 0 || keep_first < 0 || softcap < 0.0f || !(scale > 0.0f))
+    return PKV_ERR_SIZE;
   if (num_splits < 1 || num_splits > 8 || n_work > 65535 || n_kv > 65535) return PKV_ERR_LIMIT;
   if (max_entry_tokens * (n_heads / n_kv) > DT_ROWS) return PKV_ERR_LIMIT;
   const long long pool_rows = n_pages * n_kv * page_size;
@@ -450,7 +466,9 @@ PKV_EXPORT int pkv_attention_decode_tma(const void* qkv, int q_row_stride, void*
   for (int i = 0; i < 31; ++i)
     if ((1 << i) == page_size) shift = i;
   DecTmaParams p{(const bf16*)qkv, q_row_stride, (bf16*)out, block_table, table_stride, seq_starts, first_pos, work_seq,
-                 n_heads, n_kv, page_size, shift, window, scale * 1.4426950408889634f, num_splits, (int)pool_rows, status, 0};
+                 n_heads, n_kv, page_size, shift, window, scale * 1.4426950408889634f, num_splits, (int)pool_rows, status, 0,
+                 keep_first, softcap * 1.4426950408889634f,
+                 softcap > 0.0f ? 2.0f * scale / softcap * 1.4426950408889634f : 0.0f};
   // room for the pushed states of the largest entry, when that fits beside two blocks per SM
   const int most_floats = (num_splits - 1) * max_entry_tokens * (n_heads / n_kv) * (hd + 2);
   if (num_splits > 1 && most_floats <= DT_LANDING_FLOATS) p.landing_floats = (most_floats + 3) / 4 * 4;
@@ -460,4 +478,15 @@ PKV_EXPORT int pkv_attention_decode_tma(const void* qkv, int q_row_stride, void*
   // behind the other's streaming (many blocks)
   if (hd == 128) return deep_ring ? launch_dec<128, 6>(map_k, map_v, p, n_work, s) : launch_dec<128, 3>(map_k, map_v, p, n_work, s);
   return deep_ring ? launch_dec<64, 6>(map_k, map_v, p, n_work, s) : launch_dec<64, 3>(map_k, map_v, p, n_work, s);
+}
+
+PKV_EXPORT int pkv_attention_decode_tma(const void* qkv, int q_row_stride, void* out, const void* k_pool,
+                                        const void* v_pool, long long n_pages, const int32_t* block_table,
+                                        int table_stride, const int32_t* seq_starts, const int32_t* first_pos,
+                                        const int32_t* work_seq, int n_work, int max_entry_tokens, int n_heads, int n_kv,
+                                        int hd, int page_size, int window, float scale, int num_splits, int deep_ring,
+                                        int* status, void* stream) {
+  return pkv_attention_decode_tma_sink(qkv, q_row_stride, out, k_pool, v_pool, n_pages, block_table, table_stride, seq_starts,
+                                       first_pos, work_seq, n_work, max_entry_tokens, n_heads, n_kv, hd, page_size, window, 0,
+                                       scale, 0.0f, num_splits, deep_ring, status, stream);
 }

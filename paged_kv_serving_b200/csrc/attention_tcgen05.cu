@@ -45,6 +45,8 @@ struct FaParams {
   int n_heads, n_kv, page_size, page_shift, window;
   float scale_log2;
   int pool_rows;                 // rows of the key/value maps; a row coordinate >= this reads zeros
+  int keep_first;                // with a window: keys at positions below this stay visible to every later query
+  float cap_log2, cap_x;         // score cap c: c * log2(e), and 2 * scale / c * log2(e); unused without a cap
   int* status;
 };
 
@@ -59,7 +61,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // group panel after panel; otherwise one copy per page and panel, and a tile lies panel after
 // panel. With pages of 16 keys the number of copies per tile is what holds this kernel back, and
 // the wide form halves it for head size 128.
-template <int HD, int KT, bool WIDE>
+//
+// CAP: scores are capped, c * tanh(score * scale / c), before the softmax; tanh(x) = 1 - 2 / (1 + e^(2x))
+// costs two more special-function operations per score.
+// A window may keep the first tokens of a sequence visible (keep_first): the tiles that hold them
+// are walked first, then the tiles of the window (one list of tiles; where the two meet, one range).
+template <int HD, int KT, bool WIDE, bool CAP>
 __global__ void __launch_bounds__(FA_THREADS, KT == 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const FaParams p) {
@@ -96,8 +103,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int qpos_first = pos0 + q0;
   const int key_hi = qpos_first + rows_valid;                                     // exclusive
   const int key_lo = p.window > 0 ? max(0, qpos_first - p.window + 1) : 0;
-  const int tile_begin = key_lo / FA_BN, tile_end = (key_hi - 1) / FA_BN;         // inclusive
-  const int n_tiles = tile_end - tile_begin + 1;
+  const int tile_end = (key_hi - 1) / FA_BN;                                      // inclusive
+  const int keep = p.window > 0 ? min(p.keep_first, key_hi) : 0;
+  int window_tile = key_lo / FA_BN, kept = (keep + FA_BN - 1) / FA_BN;
+  if (kept >= window_tile) {           // the kept tokens' tiles reach the window's: one range from where the first begins
+    if (kept > 0) window_tile = 0;
+    kept = 0;
+  }
+  const int tile_begin = window_tile, kept_tiles = kept;
+  const int n_tiles = kept_tiles + tile_end - tile_begin + 1;
+  auto tile_of = [=](int j) { return j < kept_tiles ? j : tile_begin + (j - kept_tiles); };
   const int32_t* table = p.block_table + (size_t)s * p.table_stride;
 
   if (threadIdx.x == 0) {
@@ -113,7 +128,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // the block-table entries of this block's key range, read once
-  const int entry_first = p.page_shift >= 0 ? (tile_begin * FA_BN) >> p.page_shift : (tile_begin * FA_BN) / p.page_size;
+  const int first_key = kept_tiles > 0 ? 0 : tile_begin * FA_BN;
+  const int entry_first = p.page_shift >= 0 ? first_key >> p.page_shift : first_key / p.page_size;
   const int entry_last = p.page_shift >= 0 ? (key_hi - 1) >> p.page_shift : (key_hi - 1) / p.page_size;
   const bool table_cached = entry_last - entry_first + 1 <= FA_TABLE_CACHE;
   if (table_cached)
@@ -142,7 +158,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     auto load_tile = [&](int which, int j) {
       const int stage = which ? j % VSTAGES : j & 1;
       const int round = which ? j / VSTAGES : j >> 1;
-      const int tile_base = (tile_begin + j) * FA_BN;
+      const int tile_base = tile_of(j) * FA_BN;
       uint64_t* empty = which ? &v_empty[stage] : &k_empty[stage];
       uint64_t* full = which ? &v_full[stage] : &k_full[stage];
       if (lane == 0) {
@@ -156,7 +172,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         const int i = WIDE ? b : b / PANELS, pn = WIDE ? 0 : b - i * PANELS;
         const int pos = tile_base + i * p.page_size;
         int row = p.pool_rows;                               // outside the pool: zeros
-        if (pos < key_hi && pos + p.page_size > key_lo) {
+        if (pos < key_hi && (pos + p.page_size > key_lo || pos < keep)) {
           const int e = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
           const int page = table_cached ? table_cache[e - entry_first] : table[e];
           row = checked_pool_row(page, p.n_kv, kvh, p.page_size, p.pool_rows, p.status);
@@ -245,7 +261,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int buf = j & 1;
-      const int tile_base = (tile_begin + j) * FA_BN;
+      const int tile_base = tile_of(j) * FA_BN;
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[buf], (j >> 1) & 1, aborted) ? 1 : 0) != 0;
       if (!ok) break;
       tc_fence_after();
@@ -266,7 +282,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
         for (int c = 0; c < FA_BN; ++c) {
           const int kpos = tile_base + c;
-          const bool visible = kpos <= qpos && (p.window == 0 || kpos > qpos - p.window);
+          const bool visible = kpos <= qpos && (p.window == 0 || kpos > qpos - p.window || kpos < keep);
           sc[c] = visible ? sc[c] : -INFINITY;
           tmax = fmaxf(tmax, sc[c]);
         }
@@ -278,7 +294,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
         tmax = fmaxf(fmaxf(t0, t1), fmaxf(t2, t3));
       }
-      tmax *= p.scale_log2;
+      // the capped score in log2 units; -inf (masked) stays -inf
+      auto capped = [&](float raw) {
+        const float e = ex2_approx(raw * p.cap_x);
+        const float t = 1.0f - __fdividef(2.0f, 1.0f + e);
+        return raw == -INFINITY ? -INFINITY : p.cap_log2 * t;
+      };
+      if (CAP) tmax = capped(tmax);        // the cap grows with the score: the maximum may be capped after it was found
+      else tmax *= p.scale_log2;
       // the reference maximum moves only when the row's maximum outgrew it by 2^8
       const bool grow = tmax > m_ref + FA_RESCALE_STEP;
       const float m_new = grow ? tmax : m_ref;
@@ -289,10 +312,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       for (int c = 0; c < FA_BN; c += 4) {
         // p = 2^(score * scale - max): one multiply-add and one ex2 per element; a masked score
         // (-inf) gives exactly 0
-        sc[c] = ex2_approx(fmaf(sc[c], p.scale_log2, neg_shift));
-        sc[c + 1] = ex2_approx(fmaf(sc[c + 1], p.scale_log2, neg_shift));
-        sc[c + 2] = ex2_approx(fmaf(sc[c + 2], p.scale_log2, neg_shift));
-        sc[c + 3] = ex2_approx(fmaf(sc[c + 3], p.scale_log2, neg_shift));
+        if (CAP) {
+          sc[c] = ex2_approx(capped(sc[c]) + neg_shift);
+          sc[c + 1] = ex2_approx(capped(sc[c + 1]) + neg_shift);
+          sc[c + 2] = ex2_approx(capped(sc[c + 2]) + neg_shift);
+          sc[c + 3] = ex2_approx(capped(sc[c + 3]) + neg_shift);
+        } else {
+          sc[c] = ex2_approx(fmaf(sc[c], p.scale_log2, neg_shift));
+          sc[c + 1] = ex2_approx(fmaf(sc[c + 1], p.scale_log2, neg_shift));
+          sc[c + 2] = ex2_approx(fmaf(sc[c + 2], p.scale_log2, neg_shift));
+          sc[c + 3] = ex2_approx(fmaf(sc[c + 3], p.scale_log2, neg_shift));
+        }
         s0 += sc[c]; s1 += sc[c + 1]; s2 += sc[c + 2]; s3 += sc[c + 3];
       }
       const float sum = (s0 + s1) + (s2 + s3);
@@ -415,20 +445,27 @@ static bool pool_map(const void* base, long long rows, int hd, int box_rows, int
   return true;
 }
 
-template <int HD, int KT, bool WIDE>
-static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int n_work,
+template <int HD, int KT, bool WIDE, bool CAP>
+static int launch_fa_form(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int n_work,
                      cudaStream_t s) {
   // the query tile, two key tiles, one or two value tiles, the probabilities, and room to align
   const size_t panels = HD / 64;
   const size_t smem = panels * 128 * 128 + (2 + (KT == 64 ? 1 : 2)) * panels * KT * 128 + (size_t)(KT / 64) * 128 * 128 + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<HD, KT, WIDE, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attention_tcgen05_kernel<HD, KT, WIDE><<<n_work * p.n_heads, FA_THREADS, smem, s>>>(mq, mk, mv, p);
+  attention_tcgen05_kernel<HD, KT, WIDE, CAP><<<n_work * p.n_heads, FA_THREADS, smem, s>>>(mq, mk, mv, p);
   return launch_status();
+}
+
+template <int HD, int KT, bool WIDE>
+static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int n_work,
+                     cudaStream_t s) {
+  if (p.cap_log2 > 0.0f) return launch_fa_form<HD, KT, WIDE, true>(mq, mk, mv, p, n_work, s);
+  return launch_fa_form<HD, KT, WIDE, false>(mq, mk, mv, p, n_work, s);
 }
 
 }  // namespace pkv
@@ -445,15 +482,18 @@ PKV_EXPORT int pkv_attention_tcgen05_supports(int hd, int page_size, int q_row_s
 
 PKV_EXPORT int pkv_attention_tcgen05_rows() { return FA_BM; }
 
-PKV_EXPORT int pkv_attention_prefill_tcgen05(const void* qkv, int q_row_stride, int n_tokens, void* out,
-                                             const void* k_pool, const void* v_pool, long long n_pages,
-                                             const int32_t* block_table, int table_stride, const int32_t* seq_starts,
-                                             const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_q0,
-                                             int n_work, int n_heads, int n_kv, int hd, int page_size, int window,
-                                             float scale, int* status, void* stream) {
+// keep_first: with a window, keys below this position stay visible; softcap: scores are capped as
+// softcap * tanh(score * scale / softcap) (0: no cap).
+PKV_EXPORT int pkv_attention_prefill_tcgen05_sink(const void* qkv, int q_row_stride, int n_tokens, void* out,
+                                                  const void* k_pool, const void* v_pool, long long n_pages,
+                                                  const int32_t* block_table, int table_stride, const int32_t* seq_starts,
+                                                  const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_q0,
+                                                  int n_work, int n_heads, int n_kv, int hd, int page_size, int window,
+                                                  int keep_first, float scale, float softcap, int* status, void* stream) {
   if (n_work <= 0) return 0;
   if (!pkv_attention_tcgen05_supports(hd, page_size, q_row_stride)) return PKV_ERR_LIMIT;
-  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || window < 0) return PKV_ERR_SIZE;
+  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || window < 0 || keep_first < 0 || softcap < 0.0f || !(scale > 0.0f))
+    return PKV_ERR_SIZE;
   const long long pool_rows = n_pages * n_kv * page_size;
   if (pool_rows >= (1LL << 31) - page_size || (long long)n_work * n_heads >= (1LL << 31)) return PKV_ERR_LIMIT;
   if ((uintptr_t)qkv % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 16) return PKV_ERR_ALIGN;
@@ -473,7 +513,8 @@ PKV_EXPORT int pkv_attention_prefill_tcgen05(const void* qkv, int q_row_stride, 
   for (int i = 0; i < 31; ++i)
     if ((1 << i) == page_size) shift = i;
   FaParams p{(bf16*)out, block_table, table_stride, seq_starts, first_pos, work_seq, work_q0, n_heads, n_kv, page_size,
-             shift, window, scale * 1.4426950408889634f, (int)pool_rows, status};
+             shift, window, scale * 1.4426950408889634f, (int)pool_rows, keep_first, softcap * 1.4426950408889634f,
+             softcap > 0.0f ? 2.0f * scale / softcap * 1.4426950408889634f : 0.0f, status};
   cudaStream_t s = (cudaStream_t)stream;
   // tiles of 64 keys (two blocks to an SM) wherever a page fits one
   if (page_size <= 64) {
@@ -484,6 +525,17 @@ PKV_EXPORT int pkv_attention_prefill_tcgen05(const void* qkv, int q_row_stride, 
   if (hd == 128 && wide) return launch_fa<128, 128, true>(map_q, map_k, map_v, p, n_work, s);
   if (hd == 128) return launch_fa<128, 128, false>(map_q, map_k, map_v, p, n_work, s);
   return launch_fa<64, 128, false>(map_q, map_k, map_v, p, n_work, s);
+}
+
+PKV_EXPORT int pkv_attention_prefill_tcgen05(const void* qkv, int q_row_stride, int n_tokens, void* out,
+                                             const void* k_pool, const void* v_pool, long long n_pages,
+                                             const int32_t* block_table, int table_stride, const int32_t* seq_starts,
+                                             const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_q0,
+                                             int n_work, int n_heads, int n_kv, int hd, int page_size, int window,
+                                             float scale, int* status, void* stream) {
+  return pkv_attention_prefill_tcgen05_sink(qkv, q_row_stride, n_tokens, out, k_pool, v_pool, n_pages, block_table, table_stride,
+                                            seq_starts, first_pos, work_seq, work_q0, n_work, n_heads, n_kv, hd, page_size,
+                                            window, 0, scale, 0.0f, status, stream);
 }
 
 // For comparisons and tests: non-zero makes the kernel fetch one copy per page and panel even

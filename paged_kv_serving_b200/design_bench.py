@@ -1,6 +1,6 @@
 """Prefill and decode throughput of one architecture at layer sizes of a real model (random
 weights), with the time of every kernel of a step against its roofline. ``bench.py --design``
-runs it for the Revupel design and, at equal sizes, for the Llama-style decoder.
+runs it for the Revupel or the Tiburax design and, at equal sizes, for the models it is compared with.
 
 A step runs through ``ModelRunner.step``. For the kernel table one eager step is run with every
 kernel call of ``ops`` / ``ops.mixer_ops`` and every library product bracketed by CUDA events on
@@ -14,7 +14,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-__all__ = ["SIZES", "llama_like", "measure", "revupel_config"]
+__all__ = ["SIZES", "TIBURAX_SIZES", "llama_like", "measure", "revupel_config", "tiburax_config"]
 
 #: name -> sizes of a Revupel model whose layers resemble a served model's (latent attention of
 #: the kind with a compressed cache, an mLSTM block, eight experts of which two run, a dense block)
@@ -40,6 +40,33 @@ def revupel_config(size: str) -> dict:
         layers += [{**attention, "mlp": moe}, {**recurrent, "mlp": dense}]
     return {"architecture": "Revupel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "canon": {"taps": 4},
             "token_side": {"dim": z["side"]}, "layers": layers}
+
+
+#: name -> sizes of a Tiburax model at the same width, layer count and expert sizes: attention over
+#: a window with kept first tokens (grouped keys, heads of 128), a Mamba block with 16 state
+#: coordinates per channel, eight gated experts of which two run beside a shared one
+TIBURAX_SIZES = {
+    "1b": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep=4, inner=4096, state=16, dt_rank=128,
+               experts=8, top=2, expert_ff=2048, shared_ff=2048, vocab=32000, pairs=2),
+    "7b": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, window=1024, keep=4, inner=8192, state=16, dt_rank=256,
+               experts=8, top=2, expert_ff=3584, shared_ff=3584, vocab=32000, pairs=2),
+}
+
+
+def tiburax_config(size: str) -> dict:
+    z = TIBURAX_SIZES[size]
+    attention = {"type": "attention", "mixer": {
+        "heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+        "softcap": 50.0, "v_mix": True, "mask": {"size": z["window"], "keep_first": z["keep"]},
+        "rot": {"base": 10000.0, "dims": z["dim"], "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+    recurrent = {"type": "mamba1", "mixer": {"inner": z["inner"], "state": z["state"], "dt_rank": z["dt_rank"], "conv": 4}}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
+           "shared": {"ff": z["shared_ff"]}}
+    layers = []
+    for _ in range(z["pairs"]):
+        layers += [{**attention, "mlp": moe}, {**recurrent, "mlp": moe}]
+    return {"architecture": "Tiburax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(z["width"]) ** 0.5}, "layers": layers}
 
 
 def llama_like(size: str) -> dict:
@@ -93,7 +120,8 @@ class _KernelTimes:
                      "gemm_small_m", "gemm_tcgen05", "finish_norm"):
             self._wrap(ops, name, "kernel")
         for name in ("bias_act", "residual_add", "act_times_table", "route_top", "expert_act", "conv_residual", "mlstm",
-                     "latent_prepare", "latent_attention", "latent_attention_mma"):
+                     "latent_prepare", "latent_attention", "latent_attention_mma", "norm_residual", "expert_gated_act",
+                     "qkv_prepare", "attention_sink", "selective_scan"):
             self._wrap(mixer_ops, name, "kernel")
         self._wrap(gemm, "matmul", "product")
         self._wrap(torch, "bmm", "product")
@@ -178,6 +206,34 @@ def measure(config: dict, peaks: dict, *, prefill_tokens: int = 2048, batch: int
         heads, dim, vdim = args[13], args[14], args[15]
         return _bytes_of((args[0], out)) * 2, 4.0 * args[0].shape[0] * heads * dim * vdim
 
+    def window_keys(window: int, keep: int) -> float:
+        """(query, key) pairs a window with kept first tokens lets through, for the step at hand."""
+        if shape["tokens"] == shape["cache_tokens"]:              # one prompt from position 0
+            n = shape["tokens"]
+            if not window or window >= n:
+                return n * (n + 1) / 2.0
+            return window * (window + 1) / 2.0 + (n - window) * float(window + keep)
+        per_row = shape["cache_tokens"] / max(shape["tokens"], 1)
+        return shape["tokens"] * float(min(per_row, window + keep) if window else per_row)
+
+    def sink_cost(args, out):
+        # attention_sink(q, k_pool, v_pool, table, starts, first, work_seq, work_row0, H, G, dim, vdim, page, window, keep, ...)
+        heads, groups, dim, vdim, window, keep = args[8], args[9], args[10], args[11], args[13], args[14]
+        pairs = window_keys(window, keep)
+        cached = shape["cache_tokens"]                            # a prompt reads every key of its cache once
+        if shape["tokens"] != shape["cache_tokens"]:
+            per_row = shape["cache_tokens"] / max(shape["tokens"], 1)
+            cached = shape["tokens"] * (min(per_row, window + keep) if window else per_row)
+        moved = cached * groups * (dim + vdim) * 2 + out.numel() * out.element_size() * 2
+        return moved, 2.0 * heads * (dim + vdim) * pairs
+
+    def scan_cost(args, out):
+        # per token and channel: 2 state updates and sums per state coordinate on the float32 pipe; bytes: x, z, dt, out
+        x, dt_pre, a = args[0], args[2], args[7]
+        moved = x.numel() * (2 * x.element_size() + 4) + out.numel() * out.element_size()
+        return moved, 0.0
+
+    cost.update({"attention_sink": sink_cost, "selective_scan": scan_cost})
     cost.update({"latent_attention": latent_cost, "latent_attention_mma": latent_cost,
                  "attention_prefill_tcgen05": llama_prefill_cost, "attention_prefill_bf16": llama_prefill_cost,
                  "attention_decode_tma": llama_decode_cost, "attention_decode_flat": llama_decode_cost,

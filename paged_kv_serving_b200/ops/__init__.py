@@ -355,21 +355,23 @@ def attention_tcgen05_rows() -> int:
 def attention_prefill_tcgen05(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                               block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor,
                               work_seq: torch.Tensor, work_q0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
-                              page_size: int, window: int, scale: float, status: torch.Tensor) -> None:
+                              page_size: int, window: int, scale: float, status: torch.Tensor, keep_first: int = 0,
+                              softcap: float = 0.0) -> None:
     """Prefill attention on tcgen05 tensor cores with TMA page loads; writes the rows of its work
-    items (blocks of 128 queries) into ``out``."""
+    items (blocks of 128 queries) into ``out``. With a window, keys below position ``keep_first``
+    stay visible; ``softcap`` ``c > 0`` caps the scores as ``c * tanh(score * scale / c)``."""
     for name, t in (("qkv", qkv), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
         _need(t, torch.bfloat16, name)
     for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
                     ("work_seq", work_seq), ("work_q0", work_q0), ("status", status)):
         _need(t, torch.int32, name)
-    fn = _fn("attention_tcgen05", "pkv_attention_prefill_tcgen05",
+    fn = _fn("attention_tcgen05", "pkv_attention_prefill_tcgen05_sink",
              [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
-              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p])
     _check(fn(_ptr(qkv), qkv.shape[1], qkv.shape[0], _ptr(out), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0],
               _ptr(block_table), block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq),
-              _ptr(work_q0), work_seq.numel(), n_heads, n_kv, head_dim, page_size, int(window), float(scale),
-              _ptr(status), _stream()), "attention_prefill_tcgen05")
+              _ptr(work_q0), work_seq.numel(), n_heads, n_kv, head_dim, page_size, int(window), int(keep_first),
+              float(scale), float(softcap), _ptr(status), _stream()), "attention_prefill_tcgen05")
 
 
 _DECODE_TMA_BLOCKS: dict[tuple[int, bool], int] = {}
@@ -415,22 +417,23 @@ def attention_decode_tma(qkv: torch.Tensor, out: torch.Tensor, k_pool: torch.Ten
                          block_table: torch.Tensor, seq_starts: torch.Tensor, first_pos: torch.Tensor,
                          work_seq: torch.Tensor, max_entry_tokens: int, n_heads: int, n_kv: int, head_dim: int,
                          page_size: int, window: int, scale: float, num_splits: int, status: torch.Tensor,
-                         deep_ring: bool = True) -> None:
+                         deep_ring: bool = True, keep_first: int = 0, softcap: float = 0.0) -> None:
     """Split-KV decode attention with TMA page loads into a ring of stages (at most 8 splits,
     merged inside a thread-block cluster); writes the rows of its entries into ``out``.
-    ``deep_ring``: six stages and one block per SM (few blocks), else three stages and two."""
+    ``deep_ring``: six stages and one block per SM (few blocks), else three stages and two.
+    ``keep_first`` and ``softcap`` as in ``attention_prefill_tcgen05``."""
     for name, t in (("qkv", qkv), ("out", out), ("k_pool", k_pool), ("v_pool", v_pool)):
         _need(t, torch.bfloat16, name)
     for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
                     ("work_seq", work_seq), ("status", status)):
         _need(t, torch.int32, name)
-    fn = _fn("attention_decode_tma", "pkv_attention_decode_tma",
+    fn = _fn("attention_decode_tma", "pkv_attention_decode_tma_sink",
              [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p, c_void_p])
     _check(fn(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(k_pool), _ptr(v_pool), k_pool.shape[0], _ptr(block_table),
               block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), work_seq.numel(),
-              int(max_entry_tokens), n_heads, n_kv, head_dim, page_size, int(window), float(scale), int(num_splits),
-              int(bool(deep_ring)), _ptr(status), _stream()), "attention_decode_tma")
+              int(max_entry_tokens), n_heads, n_kv, head_dim, page_size, int(window), int(keep_first), float(scale),
+              float(softcap), int(num_splits), int(bool(deep_ring)), _ptr(status), _stream()), "attention_decode_tma")
 
 
 _DECODE_FLAT_BLOCKS: dict[int, int] = {}

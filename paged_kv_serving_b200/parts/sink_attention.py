@@ -5,6 +5,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+from paged_kv_serving_b200 import ops
 from paged_kv_serving_b200.config.registry import register_part
 from paged_kv_serving_b200.ops import arena, gemm, mixer_ops
 from paged_kv_serving_b200.parts.base import CacheBinding, PagedKVRequest, ParamSpec, Part, StepContext
@@ -38,9 +39,18 @@ class SinkWindowAttention(Part):
 
     Keys are cached rotated and normalised, in pages of ``[G, page_size, dim]`` and ``[G,
     page_size, vdim]``. Angles, norms, scores, softmax and the blend are float32 arithmetic.
+
+    Kernels: one for rotation, unit norm, blend and cache write (``ops.mixer_ops.qkv_prepare``);
+    for the attention itself, in bfloat16 with keys and values of one size of 64 or 128 and pages
+    of a multiple of 8 keys, the tensor-core kernels of ``PagedAttention`` (tcgen05 for runs of
+    queries, the TMA-fed split-key kernel for entries of a few rows), which take the kept first
+    tokens as further tiles in front of the window's and cap the scores in their softmax; for
+    every other size and for float32 the general kernel ``ops.mixer_ops.attention_sink``.
     """
 
     graph_safe = True
+    #: Set to False to keep every step on the general kernel (tests compare the two).
+    USE_TENSOR_CORES = True
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
                  rotary: ScaledRotaryFrequencies | None = None, unit_norm: bool = True, eps: float = 1e-6,
@@ -65,6 +75,7 @@ class SinkWindowAttention(Part):
         self.q_cols = self.n_heads * self.dim
         self.kv_cols = self.n_kv_heads * (self.dim + self.vdim)
         self.fused_rows = _round_up(self.q_cols + self.kv_cols, 8)
+        self._fast_ok: dict = {}
 
     @property
     def group_size(self) -> int:
@@ -101,6 +112,9 @@ class SinkWindowAttention(Part):
         return (f"sink_attention/work_seq/g{self.group_size}", f"sink_attention/work_row0/g{self.group_size}")
 
     def plan_step(self, ctx: StepContext, binding: CacheBinding | None) -> None:
+        if self._fast(ctx, ctx.groups[binding.group].page_size):
+            self._plan_fast(ctx, ctx.groups[binding.group].page_size)
+            return
         seq_name, row_name = self._work_names()
         if seq_name in ctx.arena:
             return
@@ -112,6 +126,82 @@ class SinkWindowAttention(Part):
         work_row0 = (np.arange(int(blocks.sum()), dtype=np.int64) - np.repeat(starts, blocks)) * rows_per_block
         ctx.arena.add(seq_name, work_seq)
         ctx.arena.add(row_name, work_row0)
+
+    def _fast(self, ctx: StepContext, page_size: int) -> bool:
+        """Whether the tensor-core kernels serve this mixer in this step."""
+        if not self.USE_TENSOR_CORES or ctx.dtype != torch.bfloat16 or self.dim != self.vdim:
+            return False
+        key = page_size
+        if key not in self._fast_ok:
+            self._fast_ok[key] = (ops.attention_tcgen05_supports(self.dim, page_size, self.fused_rows)
+                                  and ops.attention_decode_tma_supports(self.dim, page_size, self.fused_rows))
+        return self._fast_ok[key]
+
+    def _fast_key(self, page_size: int) -> str:
+        return (f"sink_attention/fast/h{self.n_heads}k{self.n_kv_heads}d{self.dim}w{self.window or 0}s{self.keep_first}"
+                f"p{page_size}")
+
+    def _plan_fast(self, ctx: StepContext, page_size: int) -> None:
+        """Work lists of the tensor-core kernels: entries of at most 16 rows per key/value head go to
+        the split-key decode kernel, longer ones are cut into blocks of 128 queries, heaviest first."""
+        key = self._fast_key(page_size)
+        if key in ctx.scratch:
+            return
+        from paged_kv_serving_b200.parts.attention import _sm_count
+
+        block_rows = ops.attention_tcgen05_rows()
+        lens = np.asarray(ctx.seq_lens, dtype=np.int64)
+        first = np.asarray(ctx.first_positions, dtype=np.int64)
+        small = lens * self.group_size <= 16
+        decode_entries = np.nonzero(small)[0]
+        large = np.nonzero(~small)[0]
+        blocks = (lens[large] + block_rows - 1) // block_rows
+        work_seq = np.repeat(large, blocks)
+        starts = np.cumsum(blocks) - blocks
+        work_q0 = (np.arange(int(blocks.sum()), dtype=np.int64) - np.repeat(starts, blocks)) * block_rows
+        cost = first[work_seq] + work_q0
+        if self.window:
+            cost = np.minimum(cost, self.window + self.keep_first)
+        order = np.argsort(-cost, kind="stable")
+        num_splits = 1
+        if len(decode_entries):
+            longest = int((first[decode_entries] + lens[decode_entries]).max())
+            if ctx.planning_context_len is not None:
+                longest = ctx.planning_context_len
+            if self.window:
+                longest = min(longest, self.window + self.keep_first + 64)
+            tiles = max(1, -(-longest // 64))
+            resident = 2 * _sm_count(ctx.device)
+            num_splits = int(max(1, min(tiles, 8, resident // (len(decode_entries) * self.n_kv_heads))))
+            if num_splits > 4:
+                rows = int(lens[decode_entries].max()) * self.group_size
+                pushed = ops.attention_decode_tma_pushed_splits(self.dim, rows)
+                if 4 <= pushed < num_splits:
+                    num_splits = pushed
+        names = {k: f"{key}/{k}" for k in ("prefill_seq", "prefill_q0", "decode_seq")}
+        ctx.arena.add(names["prefill_seq"], work_seq[order] if len(order) else [0])
+        ctx.arena.add(names["prefill_q0"], work_q0[order] if len(order) else [0])
+        ctx.arena.add(names["decode_seq"], decode_entries if len(decode_entries) else [0])
+        ctx.scratch[key] = {"names": names, "n_prefill": int(len(order)), "n_decode": int(len(decode_entries)),
+                            "max_small_tokens": int(lens[decode_entries].max()) if len(decode_entries) else 0,
+                            "num_splits": num_splits}
+
+    def _attend_fast(self, qkv: torch.Tensor, ctx: StepContext, group, k_pool, v_pool) -> torch.Tensor:
+        plan = ctx.scratch[self._fast_key(group.page_size)]
+        names = plan["names"]
+        out = arena.empty((qkv.shape[0], self.n_heads * self.vdim), qkv.dtype, qkv.device)
+        table, starts, first = ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS)
+        if plan["n_prefill"]:
+            ops.attention_prefill_tcgen05(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["prefill_seq"]),
+                                          ctx.ints(names["prefill_q0"]), self.n_heads, self.n_kv_heads, self.dim,
+                                          group.page_size, self.window or 0, self.scale, ctx.status,
+                                          keep_first=self.keep_first, softcap=self.softcap)
+        if plan["n_decode"]:
+            ops.attention_decode_tma(qkv, out, k_pool, v_pool, table, starts, first, ctx.ints(names["decode_seq"]),
+                                     plan["max_small_tokens"], self.n_heads, self.n_kv_heads, self.dim, group.page_size,
+                                     self.window or 0, self.scale, plan["num_splits"], ctx.status, False,
+                                     keep_first=self.keep_first, softcap=self.softcap)
+        return out
 
     def forward(self, x: torch.Tensor, ctx: StepContext, binding: CacheBinding) -> torch.Tensor:
         group = ctx.groups[binding.group]
@@ -135,6 +225,8 @@ class SinkWindowAttention(Part):
             rotary.dims if rotary else 0, rotary.amplitude if rotary else 1.0, self.eps, self.unit_norm, k_pool, v_pool,
             slots, self.n_heads, self.n_kv_heads, self.dim, self.vdim, group.page_size, ctx.status,
             v_other=other, blend=self.blend if other is not None else None, keep_values=shared)
+        if self._fast(ctx, group.page_size):
+            return gemm.linear(self._attend_fast(qkv, ctx, group, k_pool, v_pool), self.o, out_dtype=torch.float32)
         seq_name, row_name = self._work_names()
         attended = mixer_ops.attention_sink(
             qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),

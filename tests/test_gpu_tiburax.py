@@ -541,3 +541,54 @@ def test_a_decisive_router_picks_the_plain_experts(dtype):
         gap = gap - gap.mean(axis=-1, keepdims=True)
         error = np.sqrt((gap ** 2).mean(axis=-1)) / want.std()
         assert int((error > 0.1).sum()) <= 3, f"{int((error > 0.1).sum())} rows look like another expert"
+
+
+# --- the tensor-core attention kernels (bfloat16, keys and values of one size of 64 or 128) --------------
+
+
+def _sharp(dim, heads, kv_heads, window, keep, softcap, rot_dims):
+    return _attention(heads, kv_heads, dim, dim, window=window, keep=keep, rot_dims=rot_dims, softcap=softcap, scale=4.0 * dim ** -0.5,
+                      v_mix=False)
+
+
+FAST = {
+    "heads_of_64_window_past_a_tile": (_sharp(64, 4, 2, 70, 5, 30.0, 32), 8),
+    "heads_of_128_kept_tokens_past_a_tile": (_sharp(128, 2, 1, 150, 66, 50.0, 128), 16),
+    "window_and_kept_tokens_on_tile_borders": (_sharp(64, 2, 1, 128, 64, 20.0, 64), 16),
+    "kept_tokens_meet_the_window": (_sharp(64, 2, 2, 100, 40, 0.0, 16), 32),
+    "no_window_tight_cap": (_sharp(128, 4, 4, 100000, 0, 3.0, 64), 64),
+    "window_of_three": (_sharp(64, 8, 2, 3, 1, 30.0, 32), 8),
+}
+
+
+@pytest.mark.parametrize("what", sorted(FAST))
+def test_tensor_core_attention_with_window_kept_tokens_and_cap(what):
+    from paged_kv_serving_b200.parts import SinkWindowAttention
+
+    mixer, page = FAST[what]
+    config = _model([_layer(mixer, None), _layer(copy.deepcopy(mixer), None)], vocab=120, width=64, scale=2.0)
+    config["layers"][0]["mixer"]["v_mix"] = config["layers"][1]["mixer"]["v_mix"] = True
+    tensors = random_tensors(config, seed=61, scale=1.5)
+    tokens = tokens_for(config, 330, seed=62)
+    want = plain_logits(config, tensors, tokens)
+
+    def run(tensor_cores):
+        before = SinkWindowAttention.USE_TENSOR_CORES
+        SinkWindowAttention.USE_TENSOR_CORES = tensor_cores
+        try:
+            session = session_for(config, tensors, "bfloat16", max_tokens=384, page=page)
+            assert session.model.layout.blocks[0].mixer._fast(type("C", (), {"dtype": torch.bfloat16})(), page) == tensor_cores
+            rows = [session.step([{"id": "r", "tokens": tokens[:200], "want": list(range(200))}]),
+                    session.step([{"id": "r", "tokens": tokens[200:240], "want": list(range(40))}]),
+                    session.step([{"id": "r", "tokens": tokens[240:243], "want": [0, 1, 2]}])]
+            rows += [session.step([{"id": "r", "tokens": [t], "want": [0]}]) for t in tokens[243:]]
+            return np.concatenate(rows)
+        finally:
+            SinkWindowAttention.USE_TENSOR_CORES = before
+
+    fast, general = run(True), run(False)
+    for name, got in (("tensor cores", fast), ("general kernel", general)):
+        gap = got - want
+        gap = gap - gap.mean(axis=-1, keepdims=True)
+        error = np.sqrt((gap ** 2).mean(axis=-1)) / want.std()
+        assert float(np.median(error)) <= 0.03 and float(error.max()) <= 0.15, f"{what}, {name}: rows off by up to {error.max():.3e}"
