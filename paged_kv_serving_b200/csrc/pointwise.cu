@@ -385,8 +385,9 @@ PKV_EXPORT int pkv_route_top(const float* logits, int ld, const float* bias, flo
                              int renormalise, void* stream) {
   if (tokens <= 0) return 0;
   if (experts < 1 || top < 1 || top > experts || ld < experts) return PKV_ERR_SIZE;
-  route_top_kernel<<<blocks_for(tokens, 128), 128, 0, (cudaStream_t)stream>>>(logits, ld, bias, weights, tokens, experts, top,
-                                                                              renormalise);
+  // a token a thread, little work each: small blocks spread a prompt's tokens over many SMs
+  route_top_kernel<<<blocks_for(tokens, 32), 32, 0, (cudaStream_t)stream>>>(logits, ld, bias, weights, tokens, experts, top,
+                                                                            renormalise);
   return launch_status();
 }
 

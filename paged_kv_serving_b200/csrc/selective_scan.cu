@@ -9,17 +9,27 @@
 // recurrence is float32: the step sizes, the decays, B and C (they arrive as the float32 result
 // of their projection), the state. x and z are activations in the compute type.
 //
-// A team of L lanes (a power of two, at most a warp) owns one channel; each lane keeps up to
-// SCAN_REGS state coordinates n = lane_in_team + r * L in registers. A block of SCAN_THREADS
-// threads takes SCAN_THREADS / L channels of one sequence and walks the portion in chunks of
-// SCAN_CHUNK tokens staged in shared memory (coalesced loads of dt, x, z, B and C).
+// A team of L lanes (a power of two, at most a warp) owns one channel; each lane keeps R state
+// coordinates n = lane_in_team + r * L in registers (R is 2, 4 or 8 by the state's size; L and R
+// are template parameters, so every index is a constant). A block of SCAN_THREADS threads takes
+// SCAN_THREADS / L channels of one sequence and walks the portion in chunks of SCAN_CHUNK tokens
+// staged in shared memory (the softplus is taken while staging). Inside a chunk the token loop is
+// unrolled and holds only what depends on the state: the decays exp(dt A) and the inputs dt x B
+// of all 16 tokens are independent of it and are scheduled ahead, so the chain through the state
+// is one multiply-add a token. Each lane's share of y stays in registers until the chunk ends;
+// then the shares of a team are added (shuffles) and left in shared memory, and all threads
+// together add D x, apply the gate and store the chunk's outputs.
+// A chunk that the portion does not fill is padded with dt = 0 and x = 0, which leave the state
+// as it is (decay 1, input 0); coordinates beyond the state's size are padded with B = C = 0.
+// Blocks are small (two warps) so that a prompt's few thousand lanes still spread over all SMs
+// and one block's staging overlaps another's arithmetic.
 #include "common.cuh"
 
 namespace pkv {
 
-constexpr int SCAN_THREADS = 128;
-constexpr int SCAN_REGS = 8;
+constexpr int SCAN_THREADS = 64;
 constexpr int SCAN_CHUNK = 16;
+constexpr int SCAN_MAX_REGS = 8;
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 
@@ -27,96 +37,132 @@ struct ScanParams {
   int inner, state;
   int ld_x, ld_z, ld_dt, ld_bc;   // row strides (elements)
   int b_at, c_at;                 // columns of B and C in the float32 projection
-  int lanes;                      // L
 };
 
-template <typename X>
+template <typename X, int L, int R>
 __global__ void __launch_bounds__(SCAN_THREADS)
 selective_scan_kernel(const X* __restrict__ x, const X* __restrict__ z, const float* __restrict__ dt_pre,
                       const float* __restrict__ dt_bias, const float* __restrict__ bc, const float* __restrict__ a,
                       const float* __restrict__ d_skip, float* __restrict__ state, const int32_t* __restrict__ seq_starts,
                       const int32_t* __restrict__ state_slots, X* __restrict__ out, ScanParams p) {
-  extern __shared__ float scan_smem[];
-  const int L = p.lanes;
-  const int channels = SCAN_THREADS / L;          // channels of this block
-  float* dt_s = scan_smem;                        // [SCAN_CHUNK][channels]   step sizes (after softplus)
-  float* x_s = dt_s + SCAN_CHUNK * channels;      // [SCAN_CHUNK][channels]
-  float* z_s = x_s + SCAN_CHUNK * channels;       // [SCAN_CHUNK][channels]
-  float* b_s = z_s + SCAN_CHUNK * channels;       // [SCAN_CHUNK][state]
-  float* c_s = b_s + SCAN_CHUNK * p.state;        // [SCAN_CHUNK][state]
+  constexpr int CHANNELS = SCAN_THREADS / L;      // channels of this block
+  constexpr int PADDED = L * R;                   // state coordinates a team covers (>= state)
+  __shared__ float dt_s[SCAN_CHUNK * CHANNELS];   // step sizes (after softplus)
+  __shared__ float x_s[SCAN_CHUNK * CHANNELS];
+  __shared__ float z_s[SCAN_CHUNK * CHANNELS];
+  __shared__ float y_s[SCAN_CHUNK * CHANNELS];
+  __shared__ float b_s[SCAN_CHUNK * PADDED];
+  __shared__ float c_s[SCAN_CHUNK * PADDED];
 
   const int s = blockIdx.y;
   const int start = seq_starts[s], n_tokens = seq_starts[s + 1] - start;
   const int slot = state_slots[s];
-  const int c0 = blockIdx.x * channels;
-  const int team = threadIdx.x / L, lane = threadIdx.x - team * L;
+  const int c0 = blockIdx.x * CHANNELS;
+  const int team = threadIdx.x / L, lane = threadIdx.x % L;
   const int c = c0 + team;
   const bool live = c < p.inner;
 
-  float S[SCAN_REGS], A[SCAN_REGS];
+  float S[R], A2[R];                              // the state, and the decay rates times log2(e)
   float* mine = state + ((size_t)slot * p.inner + (live ? c : 0)) * p.state;
 #pragma unroll
-  for (int r = 0; r < SCAN_REGS; ++r) {
+  for (int r = 0; r < R; ++r) {
     const int n = lane + r * L;
     const bool has = live && n < p.state;
     S[r] = has ? mine[n] : 0.0f;
-    A[r] = has ? a[(size_t)c * p.state + n] : 0.0f;
+    A2[r] = has ? a[(size_t)c * p.state + n] * 1.4426950408889634f : 0.0f;
   }
-  const float skip = live ? d_skip[c] : 0.0f;
 
   for (int t0 = 0; t0 < n_tokens; t0 += SCAN_CHUNK) {
     const int count = min(SCAN_CHUNK, n_tokens - t0);
     __syncthreads();                               // the chunk before is consumed
-    for (int i = threadIdx.x; i < count * channels; i += SCAN_THREADS) {
-      const int j = i / channels, k = i - j * channels;
+    for (int i = threadIdx.x; i < SCAN_CHUNK * CHANNELS; i += SCAN_THREADS) {
+      const int j = i / CHANNELS, k = i % CHANNELS;
       const int ch = c0 + k;
       const size_t t = (size_t)(start + t0 + j);
       float dtv = 0.0f, xv = 0.0f, zv = 0.0f;
-      if (ch < p.inner) {
+      if (j < count && ch < p.inner) {
         dtv = softplus_f(dt_pre[t * p.ld_dt + ch] + dt_bias[ch]);
         xv = to_float(x[t * p.ld_x + ch]);
         zv = to_float(z[t * p.ld_z + ch]);
       }
-      dt_s[j * channels + k] = dtv;
-      x_s[j * channels + k] = xv;
-      z_s[j * channels + k] = zv;
+      dt_s[i] = dtv;
+      x_s[i] = xv;
+      z_s[i] = zv;
     }
-    for (int i = threadIdx.x; i < count * p.state; i += SCAN_THREADS) {
-      const int j = i / p.state, n = i - j * p.state;
+    for (int i = threadIdx.x; i < SCAN_CHUNK * PADDED; i += SCAN_THREADS) {
+      const int j = i / PADDED, n = i % PADDED;
       const size_t t = (size_t)(start + t0 + j);
-      b_s[j * p.state + n] = bc[t * p.ld_bc + p.b_at + n];
-      c_s[j * p.state + n] = bc[t * p.ld_bc + p.c_at + n];
+      const bool has = j < count && n < p.state;
+      b_s[i] = has ? bc[t * p.ld_bc + p.b_at + n] : 0.0f;
+      c_s[i] = has ? bc[t * p.ld_bc + p.c_at + n] : 0.0f;
     }
     __syncthreads();
-    for (int j = 0; j < count; ++j) {
-      const float dtv = dt_s[j * channels + team], xv = x_s[j * channels + team];
-      const float dx = dtv * xv;
-      const float* bj = b_s + j * p.state;
-      const float* cj = c_s + j * p.state;
-      float y = 0.0f;
+    float y[SCAN_CHUNK];
 #pragma unroll
-      for (int r = 0; r < SCAN_REGS; ++r) {
-        const int n = lane + r * L;
-        if (n < p.state) {
-          S[r] = fmaf(expf(dtv * A[r]), S[r], dx * bj[n]);
-          y = fmaf(S[r], cj[n], y);
-        }
+    for (int j = 0; j < SCAN_CHUNK; ++j) {
+      const float dtv = dt_s[j * CHANNELS + team];
+      const float dx = dtv * x_s[j * CHANNELS + team];
+      float part = 0.0f;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        S[r] = fmaf(exp2f(dtv * A2[r]), S[r], dx * b_s[j * PADDED + r * L + lane]);
+        part = fmaf(S[r], c_s[j * PADDED + r * L + lane], part);
       }
-      for (int o = L >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-      if (lane == 0 && live) {
-        const float zv = z_s[j * channels + team];
-        y = fmaf(skip, xv, y);
-        out[(size_t)(start + t0 + j) * p.inner + c] = from_float<X>(y * (zv / (1.0f + expf(-zv))));
+      y[j] = part;
+    }
+#pragma unroll
+    for (int j = 0; j < SCAN_CHUNK; ++j) {
+#pragma unroll
+      for (int o = L >> 1; o > 0; o >>= 1) y[j] += __shfl_xor_sync(0xffffffffu, y[j], o);
+      if (lane == 0) y_s[j * CHANNELS + team] = y[j];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < count * CHANNELS; i += SCAN_THREADS) {
+      const int j = i / CHANNELS, k = i % CHANNELS;
+      const int ch = c0 + k;
+      if (ch < p.inner) {
+        const float zv = z_s[i];
+        const float total = fmaf(d_skip[ch], x_s[i], y_s[i]);
+        out[(size_t)(start + t0 + j) * p.inner + ch] = from_float<X>(total * (zv / (1.0f + expf(-zv))));
       }
     }
   }
   if (live) {
 #pragma unroll
-    for (int r = 0; r < SCAN_REGS; ++r) {
+    for (int r = 0; r < R; ++r) {
       const int n = lane + r * L;
       if (n < p.state) mine[n] = S[r];
     }
   }
+}
+
+template <typename X, int L, int R>
+static int launch_scan(const void* x, const void* z, const float* dt_pre, const float* dt_bias, const float* bc, const float* a,
+                       const float* d_skip, float* state, const int32_t* seq_starts, const int32_t* state_slots, void* out,
+                       const ScanParams& p, int seqs, cudaStream_t s) {
+  constexpr int CHANNELS = SCAN_THREADS / L;
+  dim3 grid((p.inner + CHANNELS - 1) / CHANNELS, seqs);
+  selective_scan_kernel<X, L, R><<<grid, SCAN_THREADS, 0, s>>>((const X*)x, (const X*)z, dt_pre, dt_bias, bc, a, d_skip, state,
+                                                               seq_starts, state_slots, (X*)out, p);
+  return launch_status();
+}
+
+template <typename X>
+static int launch_scan_for(int n_state, const void* x, const void* z, const float* dt_pre, const float* dt_bias, const float* bc,
+                           const float* a, const float* d_skip, float* state, const int32_t* seq_starts,
+                           const int32_t* state_slots, void* out, const ScanParams& p, int seqs, cudaStream_t s) {
+#define PKV_SCAN(L, R) return launch_scan<X, L, R>(x, z, dt_pre, dt_bias, bc, a, d_skip, state, seq_starts, state_slots, out, p, seqs, s)
+  // state coordinates per lane: 2, 4 or 8, the fewest that keep a team within a warp; for the
+  // common small states that leaves several lanes (more warps in flight) per channel
+  if (n_state <= 2) PKV_SCAN(1, 2);
+  if (n_state <= 4) PKV_SCAN(2, 2);
+  if (n_state <= 8) PKV_SCAN(4, 2);
+  if (n_state <= 16) PKV_SCAN(8, 2);
+  if (n_state <= 32) PKV_SCAN(16, 2);
+  if (n_state <= 64) PKV_SCAN(32, 2);
+  if (n_state <= 128) PKV_SCAN(32, 4);
+  PKV_SCAN(32, 8);
+#undef PKV_SCAN
 }
 
 }  // namespace pkv
@@ -134,21 +180,12 @@ PKV_EXPORT int pkv_selective_scan(const void* x, int ld_x, const void* z, int ld
   if (inner < 1 || n_state < 1 || ld_x < inner || ld_z < inner || ld_dt < inner || b_at < 0 || c_at < 0 ||
       ld_bc < b_at + n_state || ld_bc < c_at + n_state)
     return PKV_ERR_SIZE;
-  if (n_state > 32 * SCAN_REGS || seqs > 65535) return PKV_ERR_LIMIT;
-  int lanes = 1;
-  while (lanes * SCAN_REGS < n_state) lanes <<= 1;
-  const int channels = SCAN_THREADS / lanes;
-  ScanParams p{inner, n_state, ld_x, ld_z, ld_dt, ld_bc, b_at, c_at, lanes};
-  const size_t smem = (size_t)SCAN_CHUNK * (3 * channels + 2 * n_state) * sizeof(float);
-  dim3 grid((inner + channels - 1) / channels, seqs);
+  if (n_state > 32 * SCAN_MAX_REGS || seqs > 65535) return PKV_ERR_LIMIT;
+  ScanParams p{inner, n_state, ld_x, ld_z, ld_dt, ld_bc, b_at, c_at};
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == PKV_F32)
-    selective_scan_kernel<float><<<grid, SCAN_THREADS, smem, s>>>((const float*)x, (const float*)z, dt_pre, dt_bias, bc, a,
-                                                                  d_skip, state, seq_starts, state_slots, (float*)out, p);
-  else if (dtype == PKV_BF16)
-    selective_scan_kernel<bf16><<<grid, SCAN_THREADS, smem, s>>>((const bf16*)x, (const bf16*)z, dt_pre, dt_bias, bc, a, d_skip,
-                                                                 state, seq_starts, state_slots, (bf16*)out, p);
-  else
-    return PKV_ERR_DTYPE;
-  return launch_status();
+    return launch_scan_for<float>(n_state, x, z, dt_pre, dt_bias, bc, a, d_skip, state, seq_starts, state_slots, out, p, seqs, s);
+  if (dtype == PKV_BF16)
+    return launch_scan_for<bf16>(n_state, x, z, dt_pre, dt_bias, bc, a, d_skip, state, seq_starts, state_slots, out, p, seqs, s);
+  return PKV_ERR_DTYPE;
 }

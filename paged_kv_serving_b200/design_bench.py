@@ -104,7 +104,7 @@ class _KernelTimes:
                 a, b = args[0], args[1]
                 flops = 2.0 * a.numel() * b.shape[-1]
             elif name in self.attention_cost:
-                moved, flops = self.attention_cost[name](args, out)
+                moved, flops = self.attention_cost[name](tuple(args) + (kwargs,), out)     # (keyword arguments ride last)
             self.records.append((name, start, stop, moved, flops))
             return out
 
@@ -187,25 +187,6 @@ def measure(config: dict, peaks: dict, *, prefill_tokens: int = 2048, batch: int
     cost = {}
     shape = {"tokens": 0, "keys": 0.0}
 
-    def latent_cost(args, out):
-        heads, rank = out.shape[0], out.shape[2]
-        dk = args[4].shape[-1]
-        flops = 2.0 * heads * shape["keys"] * (dk + rank)
-        moved = shape["cache_tokens"] * dk * 2 + _bytes_of((args[0], out))
-        return moved, flops
-
-    def llama_prefill_cost(args, out):
-        heads, hd = args[9], args[11]
-        return _bytes_of((args[0], out)), 4.0 * heads * hd * shape["keys"]
-
-    def llama_decode_cost(args, out):
-        kv, hd = args[10], args[11]
-        return shape["cache_tokens"] * kv * hd * 2 * 2 + _bytes_of((args[0], out)), 4.0 * args[9] * hd * shape["keys"]
-
-    def mlstm_cost(args, out):
-        heads, dim, vdim = args[13], args[14], args[15]
-        return _bytes_of((args[0], out)) * 2, 4.0 * args[0].shape[0] * heads * dim * vdim
-
     def window_keys(window: int, keep: int) -> float:
         """(query, key) pairs a window with kept first tokens lets through, for the step at hand."""
         if shape["tokens"] == shape["cache_tokens"]:              # one prompt from position 0
@@ -215,6 +196,26 @@ def measure(config: dict, peaks: dict, *, prefill_tokens: int = 2048, batch: int
             return window * (window + 1) / 2.0 + (n - window) * float(window + keep)
         per_row = shape["cache_tokens"] / max(shape["tokens"], 1)
         return shape["tokens"] * float(min(per_row, window + keep) if window else per_row)
+
+    def latent_cost(args, out):
+        heads, rank = out.shape[0], out.shape[2]
+        dk = args[4].shape[-1]
+        flops = 2.0 * heads * shape["keys"] * (dk + rank)
+        moved = shape["cache_tokens"] * dk * 2 + _bytes_of((args[0], out))
+        return moved, flops
+
+    def llama_prefill_cost(args, out):
+        heads, hd, window, keep = args[9], args[11], args[13], args[-1].get("keep_first", 0)
+        return _bytes_of((args[0], out)), 4.0 * heads * hd * window_keys(window, keep)
+
+    def llama_decode_cost(args, out):
+        kv, hd, window, keep = args[10], args[11], args[13], args[-1].get("keep_first", 0)
+        pairs = window_keys(window, keep)
+        return pairs * kv * hd * 2 * 2 + _bytes_of((args[0], out)), 4.0 * args[9] * hd * pairs
+
+    def mlstm_cost(args, out):
+        heads, dim, vdim = args[13], args[14], args[15]
+        return _bytes_of((args[0], out)) * 2, 4.0 * args[0].shape[0] * heads * dim * vdim
 
     def sink_cost(args, out):
         # attention_sink(q, k_pool, v_pool, table, starts, first, work_seq, work_row0, H, G, dim, vdim, page, window, keep, ...)
