@@ -62,14 +62,14 @@ selective_scan_kernel(const X* __restrict__ x, const X* __restrict__ z, const fl
   const int c = c0 + team;
   const bool live = c < p.inner;
 
-  float S[R], A2[R];                              // the state, and the decay rates times log2(e)
+  float S[R], A[R];                               // the state and the decay rates
   float* mine = state + ((size_t)slot * p.inner + (live ? c : 0)) * p.state;
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const int n = lane + r * L;
     const bool has = live && n < p.state;
     S[r] = has ? mine[n] : 0.0f;
-    A2[r] = has ? a[(size_t)c * p.state + n] * 1.4426950408889634f : 0.0f;
+    A[r] = has ? a[(size_t)c * p.state + n] : 0.0f;
   }
 
   for (int t0 = 0; t0 < n_tokens; t0 += SCAN_CHUNK) {
@@ -105,7 +105,7 @@ selective_scan_kernel(const X* __restrict__ x, const X* __restrict__ z, const fl
       float part = 0.0f;
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        S[r] = fmaf(exp2f(dtv * A2[r]), S[r], dx * b_s[j * PADDED + r * L + lane]);
+        S[r] = fmaf(expf(dtv * A[r]), S[r], dx * b_s[j * PADDED + r * L + lane]);
         part = fmaf(S[r], c_s[j * PADDED + r * L + lane], part);
       }
       y[j] = part;
