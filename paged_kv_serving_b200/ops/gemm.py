@@ -53,6 +53,10 @@ PLAIN_PRODUCT_KERNEL = "library"
 #: behind (it re-reads the activations for every 16 weight rows). The LM head (float32 result, one
 #: long stream per step) stays with cuBLAS, which reaches the memory's copy rate there.
 SMALL_M_ROWS = 8
+#: Whether products that ask for it (``linear(..., few_rows_f32=True)``: the last products of sublayers whose
+#: float32 result a norm reads, router logits, the inputs of a recurrence) take that kernel's float32
+#: epilogue for decode steps.
+FEW_ROWS_F32 = True
 #: Whether that kernel is launched as a programmatic dependent where the caller asks for it
 #: (``chain=True``).
 SMALL_M_CHAINED = True
@@ -131,8 +135,12 @@ def matmul(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
 
 
 def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = None,
-           chain: bool = False) -> torch.Tensor:
+           chain: bool = False, few_rows_f32: bool = False) -> torch.Tensor:
     """``x [T, K] @ w_nk [N, K]^T``; ``out_dtype`` float32 keeps the float32 accumulator.
+
+    ``few_rows_f32``: a float32 result of the few rows of a decode step also comes from the
+    weight-streaming kernel (its float32 epilogue) where ``FEW_ROWS_F32`` allows; without it such
+    a product goes to cuBLAS, which is what the LM head wants (one long stream, at the copy rate).
 
     ``chain``: launch the decode kernel as a programmatic dependent of the kernel before it on the
     stream, so that it requests its first weights while that kernel ends. Measured inside a decode
@@ -142,6 +150,8 @@ def linear(x: torch.Tensor, w_nk: torch.Tensor, out_dtype: torch.dtype | None = 
     L1 and shared memory only when idle, and a product whose blocks arrive beside such a kernel's
     keeps the small L1 and streams at half speed, and so do the products chained after it."""
     wants_f32 = out_dtype == torch.float32
+    if wants_f32 and few_rows_f32 and FEW_ROWS_F32 and not isinstance(x, PendingNorm) and _small_m(x, w_nk, "f32"):
+        return ops.gemm_small_m(x, w_nk, "f32", chained=SMALL_M_CHAINED and chain)
     if isinstance(x, PendingNorm):
         if not wants_f32 and x.sumsq.shape[1] == 32 and _small_m(x.weighted, w_nk, "bf16"):
             return ops.gemm_small_m(x.weighted, w_nk, "bf16", chained=SMALL_M_CHAINED and chain,

@@ -226,11 +226,11 @@ class SinkWindowAttention(Part):
             slots, self.n_heads, self.n_kv_heads, self.dim, self.vdim, group.page_size, ctx.status,
             v_other=other, blend=self.blend if other is not None else None, keep_values=shared)
         if self._fast(ctx, group.page_size):
-            return gemm.linear(self._attend_fast(qkv, ctx, group, k_pool, v_pool), self.o, out_dtype=torch.float32)
+            return gemm.linear(self._attend_fast(qkv, ctx, group, k_pool, v_pool), self.o, out_dtype=torch.float32, few_rows_f32=True)
         seq_name, row_name = self._work_names()
         attended = mixer_ops.attention_sink(
             qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
             ctx.ints(seq_name), ctx.ints(row_name), self.n_heads, self.n_kv_heads, self.dim, self.vdim, group.page_size,
             self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status)
         # the float32 result of the last product goes to a norm
-        return gemm.linear(attended, self.o, out_dtype=torch.float32)
+        return gemm.linear(attended, self.o, out_dtype=torch.float32, few_rows_f32=True)
