@@ -5,7 +5,7 @@ rotates over 32 layers' worth of buffers (so that weights, keys and values come 
 a real step) and reports microseconds per launch with the achieved bandwidth or arithmetic rate.
 The sizes come from a preset of ``config/presets.py``; nothing here is used by the engine.
 
-    python kernel_bench.py [gemm] [decode-gemm] [prefill-attention] [decode-attention] [elementwise]
+    python kernel_bench.py [gemm] [decode-gemm] [prefill-attention] [decode-attention] [elementwise] [scan]
 """
 
 from __future__ import annotations
@@ -203,9 +203,32 @@ def bench_elementwise(config, page: int) -> None:
         print(f"rope_kv_store {tokens:5d} tokens: {us:6.1f} us {tokens * (h + 2 * kv) * hd * 4 / us / 1e6:5.2f} TB/s")
 
 
+def bench_scan(config, page: int) -> None:
+    """The selective scan of a Mamba mixer: one prompt of 2,048 tokens, and a decode step of 8 requests; 4,096
+    channels with 16 state coordinates (the sizes of ``bench.py --design tiburax`` at width 2,048)."""
+    from paged_kv_serving_b200.ops import mixer_ops
+
+    inner, n_state, low = 4096, 16, 160
+    a = -torch.rand((inner, n_state), device="cuda") - 0.1
+    bias = torch.full((inner,), -2.0, device="cuda")
+    skip = torch.ones((inner,), device="cuda")
+    for tokens, seqs in ((2048, 1), (8, 8)):
+        xz = [torch.randn((tokens, 2 * inner), device="cuda", dtype=torch.bfloat16) for _ in range(4)]
+        dt = [torch.randn((tokens, inner), device="cuda") for _ in range(4)]
+        bc = [torch.randn((tokens, low), device="cuda") for _ in range(4)]
+        state = torch.zeros((seqs + 1, inner, n_state), device="cuda")
+        starts = torch.arange(0, tokens + 1, tokens // seqs, device="cuda", dtype=torch.int32)
+        slots = torch.arange(seqs, device="cuda", dtype=torch.int32)
+        us = timed(lambda i: mixer_ops.selective_scan(xz[i % 4][:, :inner], xz[i % 4][:, inner:], dt[i % 4], bias, bc[i % 4], 128,
+                                                      144, a, skip, state, starts, slots))
+        moved = tokens * inner * (4 + 2 + 2 + 2)
+        print(f"selective_scan {tokens:5d} tokens in {seqs} sequences: {us:7.1f} us, {moved / us / 1e6:5.2f} TB/s of activations, "
+              f"{tokens * inner * n_state / us / 1e3:6.1f} G state updates/s")
+
+
 def main() -> int:
     cases = {"gemm": None, "decode-gemm": None, "prefill-attention": bench_prefill_attention, "decode-attention": bench_decode_attention,
-             "elementwise": bench_elementwise}
+             "elementwise": bench_elementwise, "scan": bench_scan}
     parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     parser.add_argument("cases", nargs="*", choices=[*cases, []], help="which kernels to time (default: all)")
     parser.add_argument("--preset", default="llama-3-8b")

@@ -18,7 +18,8 @@
 // of all 16 tokens are independent of it and are scheduled ahead, so the chain through the state
 // is one multiply-add a token. Each lane's share of y stays in registers until the chunk ends;
 // then the shares of a team are added (shuffles) and left in shared memory, and all threads
-// together add D x, apply the gate and store the chunk's outputs.
+// together add D x, apply the gate and store the chunk's outputs. The next chunk's inputs are
+// fetched into registers before the current chunk is computed.
 // A chunk that the portion does not fill is padded with dt = 0 and x = 0, which leave the state
 // as it is (decay 1, input 0); coordinates beyond the state's size are padded with B = C = 0.
 // Blocks are small (two warps) so that a prompt's few thousand lanes still spread over all SMs
@@ -72,31 +73,71 @@ selective_scan_kernel(const X* __restrict__ x, const X* __restrict__ z, const fl
     A[r] = has ? a[(size_t)c * p.state + n] : 0.0f;
   }
 
+  // What a thread stages of a chunk: ACT_IT elements of dt, x and z and BC_IT of B and C. They are
+  // fetched into registers one chunk ahead, so that the loads are in flight while the chunk before
+  // is computed (wide states, whose B and C would take too many registers, fetch those when staging).
+  constexpr int ACT_IT = (SCAN_CHUNK * CHANNELS + SCAN_THREADS - 1) / SCAN_THREADS;
+  constexpr int BC_IT = (SCAN_CHUNK * PADDED + SCAN_THREADS - 1) / SCAN_THREADS;
+  constexpr bool BC_AHEAD = BC_IT <= 8;
+  float f_dt[ACT_IT], f_x[ACT_IT], f_z[ACT_IT], f_b[BC_AHEAD ? BC_IT : 1], f_c[BC_AHEAD ? BC_IT : 1];
+  auto fetch = [&](int t0) {
+    const int count = min(SCAN_CHUNK, n_tokens - t0);
+#pragma unroll
+    for (int it = 0; it < ACT_IT; ++it) {
+      const int i = threadIdx.x + it * SCAN_THREADS;
+      const int j = i / CHANNELS, ch = c0 + i % CHANNELS;
+      const size_t t = (size_t)(start + t0 + j);
+      const bool has = i < SCAN_CHUNK * CHANNELS && j < count && ch < p.inner;
+      f_dt[it] = has ? dt_pre[t * p.ld_dt + ch] + dt_bias[ch] : -INFINITY;     // softplus(-inf) = 0: a padded step
+      f_x[it] = has ? to_float(x[t * p.ld_x + ch]) : 0.0f;
+      f_z[it] = has ? to_float(z[t * p.ld_z + ch]) : 0.0f;
+    }
+    if (BC_AHEAD) {
+#pragma unroll
+      for (int it = 0; it < BC_IT; ++it) {
+        const int i = threadIdx.x + it * SCAN_THREADS;
+        const int j = i / PADDED, n = i % PADDED;
+        const size_t t = (size_t)(start + t0 + j);
+        const bool has = i < SCAN_CHUNK * PADDED && j < count && n < p.state;
+        f_b[it] = has ? bc[t * p.ld_bc + p.b_at + n] : 0.0f;
+        f_c[it] = has ? bc[t * p.ld_bc + p.c_at + n] : 0.0f;
+      }
+    }
+  };
+  if (n_tokens > 0) fetch(0);
+
   for (int t0 = 0; t0 < n_tokens; t0 += SCAN_CHUNK) {
     const int count = min(SCAN_CHUNK, n_tokens - t0);
     __syncthreads();                               // the chunk before is consumed
-    for (int i = threadIdx.x; i < SCAN_CHUNK * CHANNELS; i += SCAN_THREADS) {
-      const int j = i / CHANNELS, k = i % CHANNELS;
-      const int ch = c0 + k;
-      const size_t t = (size_t)(start + t0 + j);
-      float dtv = 0.0f, xv = 0.0f, zv = 0.0f;
-      if (j < count && ch < p.inner) {
-        dtv = softplus_f(dt_pre[t * p.ld_dt + ch] + dt_bias[ch]);
-        xv = to_float(x[t * p.ld_x + ch]);
-        zv = to_float(z[t * p.ld_z + ch]);
+#pragma unroll
+    for (int it = 0; it < ACT_IT; ++it) {
+      const int i = threadIdx.x + it * SCAN_THREADS;
+      if (i < SCAN_CHUNK * CHANNELS) {
+        dt_s[i] = softplus_f(f_dt[it]);
+        x_s[i] = f_x[it];
+        z_s[i] = f_z[it];
       }
-      dt_s[i] = dtv;
-      x_s[i] = xv;
-      z_s[i] = zv;
     }
-    for (int i = threadIdx.x; i < SCAN_CHUNK * PADDED; i += SCAN_THREADS) {
-      const int j = i / PADDED, n = i % PADDED;
-      const size_t t = (size_t)(start + t0 + j);
-      const bool has = j < count && n < p.state;
-      b_s[i] = has ? bc[t * p.ld_bc + p.b_at + n] : 0.0f;
-      c_s[i] = has ? bc[t * p.ld_bc + p.c_at + n] : 0.0f;
+    if (BC_AHEAD) {
+#pragma unroll
+      for (int it = 0; it < BC_IT; ++it) {
+        const int i = threadIdx.x + it * SCAN_THREADS;
+        if (i < SCAN_CHUNK * PADDED) {
+          b_s[i] = f_b[it];
+          c_s[i] = f_c[it];
+        }
+      }
+    } else {
+      for (int i = threadIdx.x; i < SCAN_CHUNK * PADDED; i += SCAN_THREADS) {
+        const int j = i / PADDED, n = i % PADDED;
+        const size_t t = (size_t)(start + t0 + j);
+        const bool has = j < count && n < p.state;
+        b_s[i] = has ? bc[t * p.ld_bc + p.b_at + n] : 0.0f;
+        c_s[i] = has ? bc[t * p.ld_bc + p.c_at + n] : 0.0f;
+      }
     }
     __syncthreads();
+    if (t0 + SCAN_CHUNK < n_tokens) fetch(t0 + SCAN_CHUNK);
     float y[SCAN_CHUNK];
 #pragma unroll
     for (int j = 0; j < SCAN_CHUNK; ++j) {

@@ -338,36 +338,55 @@ def test_greedy_generation_through_the_entry_point(tmp_path, dtype):
                 assert row[token] >= row.max() - 0.1 * row.std(), f"token {place}: far from the plain maximum"
 
 
-def test_random_weights_mode_and_the_trace_program(tmp_path):
-    """A model folder from the random-weights mode, replayed by ``bin/trace_run`` in two cuts."""
+def test_command_line_checkpoint_generation_and_trace_program(tmp_path):
+    """The design through the command line as a user meets it: a random-weights folder from a
+    ``config.json``, greedy generation from it, and ``bin/trace_run`` replaying a trace of it."""
     import json
+    import os
     import subprocess
     import sys
     from pathlib import Path
 
-    from paged_kv_serving_b200.weights.random_init import write_random_model_folder
+    from safetensors.torch import load_file
 
-    typed, _ = _specs(CONFIGS["C"])
-    write_random_model_folder(tmp_path / "model", typed, seed=5, dtype="bfloat16", std=0.15)
-    tokens = tokens_for(CONFIGS["C"], 40, seed=6)
-    program = Path(__file__).resolve().parent.parent / "bin" / "trace_run"
+    root = Path(__file__).resolve().parent.parent
+    env = dict(os.environ, PYTHONPATH=str(root))
+    config = CONFIGS["C"]
+    model_dir, out_dir = tmp_path / "model", tmp_path / "out"
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    build = subprocess.run([sys.executable, "-m", "paged_kv_serving_b200", "build-checkpoint", "--out", str(model_dir),
+                            "--config", str(tmp_path / "config.json"), "--seed", "3", "--dtype", "bfloat16", "--std", "0.15"],
+                           capture_output=True, text=True, env=env, check=True)
+    tensors = load_file(str(model_dir / "model.safetensors"))
+    assert json.loads(build.stdout)["parameters"] == sum(t.numel() for t in tensors.values())
+    assert float(tensors["l1.norm1"].float().abs().max()) < 0.5 and float(tensors["l0.mix.A_log"].float().std()) > 0.1, \
+        "the random-weights mode draws norm weights around zero and decay logarithms with a spread"
+    run = subprocess.run([sys.executable, "-m", "paged_kv_serving_b200", "generate", "--model", str(model_dir),
+                          "--prompt-ids", "5,17,3,20", "--max-new-tokens", "6", "--dtype", "float32", "--block-size", "4"],
+                         capture_output=True, text=True, env=env, check=True)
+    line = [json.loads(text) for text in run.stdout.splitlines() if text.startswith("{")][0]
+    ids = line["samples"][0]
+    rows = plain_logits(config, tensors, [5, 17, 3, 20] + ids[:-1])[3:]
+    assert len(ids) == 6 and all(row[token] >= row.max() - 1e-4 for token, row in zip(ids, rows))
 
-    def run(steps, out):
-        lines = "\n".join(json.dumps(s) for s in steps) + "\n"
-        done = subprocess.run([sys.executable, str(program), "--model", str(tmp_path / "model"), "--dtype", "float32", "--out",
-                               str(out), "--max-tokens", "64"], input=lines, capture_output=True, text=True, timeout=600)
-        assert done.returncode == 0, done.stderr[-2000:]
-        return done.stdout
-
-    out = run([{"step": 0, "entries": [{"id": "x", "tokens": tokens, "want": [10, 39]}], "end": ["x"]}], tmp_path / "whole")
-    assert "done 0" in out
-    whole = np.fromfile(tmp_path / "whole" / "0.f32", dtype="<f4").reshape(2, -1)
-    run([{"step": 0, "entries": [{"id": "x", "tokens": tokens[:11], "want": [10]}], "end": []},
-         {"step": 1, "entries": [{"id": "x", "tokens": tokens[11:39], "want": []}], "end": []},
-         {"step": 2, "entries": [{"id": "x", "tokens": tokens[39:], "want": [0]}], "end": ["x"]}], tmp_path / "cut")
-    cut = np.concatenate([np.fromfile(tmp_path / "cut" / f"{n}.f32", dtype="<f4").reshape(1, -1) for n in (0, 2)])
-    assert not (tmp_path / "cut" / "1.f32").exists()
-    assert np.abs(cut - whole).max() <= 1e-4 * max(1.0, float(np.abs(whole).max()))
+    tokens = tokens_for(config, 30, seed=9)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": tokens[:21], "want": [0, 20]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": tokens[21:23], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": tokens[23:], "want": [6]}], "end": ["a"]}]
+    process = subprocess.Popen([str(root / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", "float32",
+                                "--out", str(out_dir), "--max-tokens", "64", "--block-size", "4"],
+                               stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
+    for record in steps:
+        process.stdin.write(json.dumps(record) + "\n")
+        process.stdin.flush()
+        assert process.stdout.readline().strip() == f"done {record['step']}"
+    process.stdin.close()
+    assert process.wait(timeout=120) == 0
+    want = plain_logits(config, tensors, tokens)
+    read = lambda step: np.fromfile(out_dir / f"{step}.f32", dtype="<f4").reshape(-1, config["vocab"])
+    assert not (out_dir / "1.f32").exists()
+    close(read(0), want[[0, 20]], "float32", "trace step 0")
+    close(read(2), want[29:30], "float32", "trace step 2")
 
 
 # --- mechanisms alone ---------------------------------------------------------------------------
