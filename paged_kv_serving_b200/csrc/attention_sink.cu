@@ -47,6 +47,8 @@ qkv_prepare_kernel(A* __restrict__ qkv, const int32_t* __restrict__ positions, c
                    const A* __restrict__ v_other, const float* __restrict__ lambda, A* __restrict__ v_keep,
                    C* __restrict__ k_pool, C* __restrict__ v_pool, const int32_t* __restrict__ slots, PrepareParams p,
                    int* __restrict__ status) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   extern __shared__ float prep_smem[];                  // [SK_WARPS][dim]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -126,6 +128,8 @@ attention_sink_kernel(const A* __restrict__ q, A* __restrict__ out, const C* __r
                       const int32_t* __restrict__ seq_starts, const int32_t* __restrict__ first_pos,
                       const int32_t* __restrict__ work_seq, const int32_t* __restrict__ work_row0, SinkParams p,
                       int* __restrict__ status) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   extern __shared__ float sk_smem[];
   const int dim = p.dim, vdim = p.vdim;
   float* q_s = sk_smem;                            // [SK_WARPS][dim]
@@ -242,9 +246,8 @@ static int launch_prepare(void* qkv, const int32_t* positions, const float* freq
                           void* v_keep, void* k_pool, void* v_pool, const int32_t* slots, const PrepareParams& p, int tokens,
                           int* status, cudaStream_t s) {
   const size_t smem = (size_t)SK_WARPS * p.dim * sizeof(float);
-  qkv_prepare_kernel<A, C><<<tokens, SK_WARPS * 32, smem, s>>>((A*)qkv, positions, freq, (const A*)v_other, lambda, (A*)v_keep,
-                                                              (C*)k_pool, (C*)v_pool, slots, p, status);
-  return launch_status();
+  return launch_kernel(qkv_prepare_kernel<A, C>, dim3(tokens), dim3(SK_WARPS * 32), smem, s, true, 0, (A*)qkv, positions, freq,
+                       (const A*)v_other, lambda, (A*)v_keep, (C*)k_pool, (C*)v_pool, slots, p, status);
 }
 
 // qkv [tokens, ld]: H query heads of `dim`, G key heads of `dim`, G value heads of `vdim`.
@@ -286,10 +289,8 @@ static int launch_sink(const void* q, void* out, const void* k_pool, const void*
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(n_work, p.n_kv);
-  attention_sink_kernel<A, C><<<grid, SK_WARPS * 32, smem, s>>>((const A*)q, (A*)out, (const C*)k_pool, (const C*)v_pool,
-                                                                block_table, seq_starts, first_pos, work_seq, work_row0, p,
-                                                                status);
-  return launch_status();
+  return launch_kernel(attention_sink_kernel<A, C>, grid, dim3(SK_WARPS * 32), smem, s, true, 0, (const A*)q, (A*)out,
+                       (const C*)k_pool, (const C*)v_pool, block_table, seq_starts, first_pos, work_seq, work_row0, p, status);
 }
 
 // Rows per work item, for the host that builds the work list.

@@ -27,6 +27,8 @@ __global__ void conv_residual_kernel(const X* __restrict__ x, int ld, const floa
                                      const int32_t* __restrict__ token_seq, const int32_t* __restrict__ seq_starts,
                                      const int32_t* __restrict__ state_slots, X* __restrict__ out, int tokens, int width,
                                      int taps, int residual, int act) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)tokens * width) return;
   const int t = (int)(i / width), c = (int)(i - (long long)t * width);
@@ -54,6 +56,8 @@ __global__ void conv_residual_bf16x8_kernel(const bf16* __restrict__ x, int ld, 
                                             const bf16* __restrict__ state, const int32_t* __restrict__ token_seq,
                                             const int32_t* __restrict__ seq_starts, const int32_t* __restrict__ state_slots,
                                             bf16* __restrict__ out, int tokens, int width, int taps, int residual, int act) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int per_row = width >> 3;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= tokens * per_row) return;
@@ -109,6 +113,8 @@ template <typename X>
 __global__ void conv_state_update_kernel(const X* __restrict__ x, int ld, X* __restrict__ state,
                                          const int32_t* __restrict__ seq_starts, const int32_t* __restrict__ state_slots,
                                          int seqs, int width, int taps) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)seqs * width) return;
   const int s = (int)(i / width), c = (int)(i - (long long)s * width);
@@ -139,27 +145,29 @@ PKV_EXPORT int pkv_conv_residual(const void* x, int dtype, int ld, const float* 
   const long long total = (long long)tokens * width;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   const unsigned state_blocks = (unsigned)(((long long)seqs * width + 255) / 256);
+  // (the tail's update waits at its top for the kernel that reads the tail to finish)
+  int rc = 0;
   if (dtype == PKV_F32) {
-    conv_residual_kernel<float><<<blocks, 256, 0, s>>>((const float*)x, ld, w, bias, (const float*)state, token_seq, seq_starts,
-                                                       state_slots, (float*)out, tokens, width, taps, residual, act);
-    if (taps > 1)
-      conv_state_update_kernel<float><<<state_blocks, 256, 0, s>>>((const float*)x, ld, (float*)state, seq_starts, state_slots,
-                                                                   seqs, width, taps);
+    rc = launch_kernel(conv_residual_kernel<float>, dim3(blocks), dim3(256), 0, s, true, 0, (const float*)x, ld, w, bias,
+                       (const float*)state, token_seq, seq_starts, state_slots, (float*)out, tokens, width, taps, residual, act);
+    if (rc == 0 && taps > 1)
+      rc = launch_kernel(conv_state_update_kernel<float>, dim3(state_blocks), dim3(256), 0, s, true, 0, (const float*)x, ld,
+                         (float*)state, seq_starts, state_slots, seqs, width, taps);
   } else if (dtype == PKV_BF16) {
     const bool wide = w_t != nullptr && ((uintptr_t)w_t & 15) == 0 && width % 8 == 0 && ld % 8 == 0 && ((uintptr_t)x & 15) == 0 &&
                       ((uintptr_t)out & 15) == 0 && (taps == 1 || ((uintptr_t)state & 15) == 0) && total / 8 < (1ll << 31);
     if (wide)
-      conv_residual_bf16x8_kernel<<<(unsigned)((total / 8 + 255) / 256), 256, 0, s>>>(
-          (const bf16*)x, ld, w_t, bias, (const bf16*)state, token_seq, seq_starts, state_slots, (bf16*)out, tokens, width, taps,
-          residual, act);
+      rc = launch_kernel(conv_residual_bf16x8_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, s, true, 0,
+                         (const bf16*)x, ld, w_t, bias, (const bf16*)state, token_seq, seq_starts, state_slots, (bf16*)out, tokens,
+                         width, taps, residual, act);
     else
-      conv_residual_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)x, ld, w, bias, (const bf16*)state, token_seq, seq_starts,
-                                                      state_slots, (bf16*)out, tokens, width, taps, residual, act);
-    if (taps > 1)
-      conv_state_update_kernel<bf16><<<state_blocks, 256, 0, s>>>((const bf16*)x, ld, (bf16*)state, seq_starts, state_slots,
-                                                                  seqs, width, taps);
+      rc = launch_kernel(conv_residual_kernel<bf16>, dim3(blocks), dim3(256), 0, s, true, 0, (const bf16*)x, ld, w, bias,
+                         (const bf16*)state, token_seq, seq_starts, state_slots, (bf16*)out, tokens, width, taps, residual, act);
+    if (rc == 0 && taps > 1)
+      rc = launch_kernel(conv_state_update_kernel<bf16>, dim3(state_blocks), dim3(256), 0, s, true, 0, (const bf16*)x, ld,
+                         (bf16*)state, seq_starts, state_slots, seqs, width, taps);
   } else {
     return PKV_ERR_DTYPE;
   }
-  return launch_status();
+  return rc;
 }

@@ -38,6 +38,8 @@ __global__ void bias_act_kernel(const X* __restrict__ x, const float* __restrict
 template <typename D, typename O>
 __global__ void residual_add_kernel(float* __restrict__ hidden, const D* __restrict__ delta,
                                     const float* __restrict__ bias, O* __restrict__ out, long long total, int cols) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   float v = hidden[i];
@@ -70,6 +72,8 @@ __global__ void act_times_table_kernel(const X* __restrict__ z, const X* __restr
 // added to the logits first.
 __global__ void route_top_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias,
                                  float* __restrict__ weights, int tokens, int experts, int top, int renormalise) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= tokens) return;
   const float* z = logits + (size_t)t * ld;
@@ -191,6 +195,8 @@ __global__ void expert_act_bf16x8_kernel(const bf16* __restrict__ up, int ld, co
 template <typename X>
 __global__ void expert_gated_act_kernel(const X* __restrict__ gu, int ld, int up_at, const float* __restrict__ weights,
                                         X* __restrict__ out, int tokens, int experts, int ff, int shared_ff, int act) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int cols = experts * ff + shared_ff;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)tokens * cols) return;
@@ -207,6 +213,8 @@ __global__ void expert_gated_act_kernel(const X* __restrict__ gu, int ld, int up
 __global__ void expert_gated_act_bf16x8_kernel(const bf16* __restrict__ gu, int ld, int up_at,
                                                const float* __restrict__ weights, bf16* __restrict__ out, int tokens,
                                                int experts, int ff, int shared_ff, int act) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   const int cols = experts * ff + shared_ff;
   const int per_row = cols >> 3;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -232,6 +240,8 @@ __global__ void expert_gated_act_bf16x8_kernel(const bf16* __restrict__ gu, int 
 template <typename D, typename O>
 __global__ void norm_residual_kernel(float* __restrict__ hidden, const D* __restrict__ delta, const float* __restrict__ weight,
                                      float eps, O* __restrict__ out, int d) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   extern __shared__ float nr_smem[];   // d floats + 32 scratch
   float* row = nr_smem;
   float* scratch = nr_smem + d;
@@ -353,7 +363,7 @@ PKV_EXPORT int pkv_residual_add(float* hidden, const void* delta, int delta_dtyp
   const long long total = rows * cols;
   if (total <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-#define PKV_RA(D, O) residual_add_kernel<D, O><<<blocks_for(total, 256), 256, 0, s>>>(hidden, (const D*)delta, bias, (O*)out, total, cols); return launch_status()
+#define PKV_RA(D, O) return launch_kernel(residual_add_kernel<D, O>, dim3(blocks_for(total, 256)), dim3(256), 0, s, true, 0, hidden, (const D*)delta, bias, (O*)out, total, cols)
   if (delta_dtype == PKV_F32 && out_dtype == PKV_F32) { PKV_RA(float, float); }
   if (delta_dtype == PKV_F32 && out_dtype == PKV_BF16) { PKV_RA(float, bf16); }
   if (delta_dtype == PKV_BF16 && out_dtype == PKV_BF16) { PKV_RA(bf16, bf16); }
@@ -386,9 +396,8 @@ PKV_EXPORT int pkv_route_top(const float* logits, int ld, const float* bias, flo
   if (tokens <= 0) return 0;
   if (experts < 1 || top < 1 || top > experts || ld < experts) return PKV_ERR_SIZE;
   // a token a thread, little work each: small blocks spread a prompt's tokens over many SMs
-  route_top_kernel<<<blocks_for(tokens, 32), 32, 0, (cudaStream_t)stream>>>(logits, ld, bias, weights, tokens, experts, top,
-                                                                            renormalise);
-  return launch_status();
+  return launch_kernel(route_top_kernel, dim3(blocks_for(tokens, 32)), dim3(32), 0, (cudaStream_t)stream, true, 0, logits, ld, bias,
+                       weights, tokens, experts, top, renormalise);
 }
 
 PKV_EXPORT int pkv_expert_gated_act(const void* gu, int dtype, int ld, int up_at, const float* weights, void* out, int tokens,
@@ -399,15 +408,15 @@ PKV_EXPORT int pkv_expert_gated_act(const void* gu, int dtype, int ld, int up_at
   if (experts < 0 || ff < 0 || shared_ff < 0 || act < 0 || act > ACT_LAST || up_at < cols || ld < up_at + cols) return PKV_ERR_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == PKV_F32) {
-    expert_gated_act_kernel<float><<<blocks_for(total, 256), 256, 0, s>>>((const float*)gu, ld, up_at, weights, (float*)out,
-                                                                          tokens, experts, ff, shared_ff, act);
+    return launch_kernel(expert_gated_act_kernel<float>, dim3(blocks_for(total, 256)), dim3(256), 0, s, true, 0, (const float*)gu, ld,
+                         up_at, weights, (float*)out, tokens, experts, ff, shared_ff, act);
   } else if (dtype == PKV_BF16 && ff % 8 == 0 && shared_ff % 8 == 0 && ld % 8 == 0 && up_at % 8 == 0 &&
              ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0) {
-    expert_gated_act_bf16x8_kernel<<<blocks_for(total / 8, 256), 256, 0, s>>>((const bf16*)gu, ld, up_at, weights, (bf16*)out,
-                                                                               tokens, experts, ff, shared_ff, act);
+    return launch_kernel(expert_gated_act_bf16x8_kernel, dim3(blocks_for(total / 8, 256)), dim3(256), 0, s, true, 0, (const bf16*)gu,
+                         ld, up_at, weights, (bf16*)out, tokens, experts, ff, shared_ff, act);
   } else if (dtype == PKV_BF16) {
-    expert_gated_act_kernel<bf16><<<blocks_for(total, 256), 256, 0, s>>>((const bf16*)gu, ld, up_at, weights, (bf16*)out,
-                                                                         tokens, experts, ff, shared_ff, act);
+    return launch_kernel(expert_gated_act_kernel<bf16>, dim3(blocks_for(total, 256)), dim3(256), 0, s, true, 0, (const bf16*)gu, ld,
+                         up_at, weights, (bf16*)out, tokens, experts, ff, shared_ff, act);
   } else {
     return PKV_ERR_DTYPE;
   }
@@ -428,8 +437,8 @@ PKV_EXPORT int pkv_norm_residual(float* hidden, const void* delta, int delta_dty
       cudaError_t e = cudaFuncSetAttribute(norm_residual_kernel<D, O>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return (int)e;                                                                               \
     }                                                                                                                    \
-    norm_residual_kernel<D, O><<<rows, threads, smem, s>>>(hidden, (const D*)delta, weight, eps, (O*)out, d);            \
-    return launch_status();                                                                                              \
+    return launch_kernel(norm_residual_kernel<D, O>, dim3(rows), dim3(threads), smem, s, true, 0, hidden, (const D*)delta,  \
+                         weight, eps, (O*)out, d);                                                                        \
   } while (0)
   if (!out) out_dtype = PKV_F32;
   if (delta_dtype == PKV_F32 && out_dtype == PKV_F32) PKV_NR(float, float);

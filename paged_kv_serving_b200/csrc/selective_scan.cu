@@ -46,6 +46,8 @@ selective_scan_kernel(const X* __restrict__ x, const X* __restrict__ z, const fl
                       const float* __restrict__ dt_bias, const float* __restrict__ bc, const float* __restrict__ a,
                       const float* __restrict__ d_skip, float* __restrict__ state, const int32_t* __restrict__ seq_starts,
                       const int32_t* __restrict__ state_slots, X* __restrict__ out, ScanParams p) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
   constexpr int CHANNELS = SCAN_THREADS / L;      // channels of this block
   constexpr int PADDED = L * R;                   // state coordinates a team covers (>= state)
   __shared__ float dt_s[SCAN_CHUNK * CHANNELS];   // step sizes (after softplus)
@@ -183,9 +185,8 @@ static int launch_scan(const void* x, const void* z, const float* dt_pre, const 
                        const ScanParams& p, int seqs, cudaStream_t s) {
   constexpr int CHANNELS = SCAN_THREADS / L;
   dim3 grid((p.inner + CHANNELS - 1) / CHANNELS, seqs);
-  selective_scan_kernel<X, L, R><<<grid, SCAN_THREADS, 0, s>>>((const X*)x, (const X*)z, dt_pre, dt_bias, bc, a, d_skip, state,
-                                                               seq_starts, state_slots, (X*)out, p);
-  return launch_status();
+  return launch_kernel(selective_scan_kernel<X, L, R>, grid, dim3(SCAN_THREADS), 0, s, true, 0, (const X*)x, (const X*)z, dt_pre,
+                       dt_bias, bc, a, d_skip, state, seq_starts, state_slots, (X*)out, p);
 }
 
 template <typename X>

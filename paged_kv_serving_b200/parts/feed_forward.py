@@ -226,10 +226,10 @@ class GatedRoutedExperts(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         from paged_kv_serving_b200.ops import mixer_ops
 
-        logits = gemm.linear(x, self.router, out_dtype=torch.float32, few_rows_f32=True)       # [tokens, experts (padded)]
+        logits = gemm.linear(x, self.router, out_dtype=torch.float32, few_rows_f32=True, chain=True)       # [tokens, experts (padded)]
         weights = mixer_ops.route_top(logits, self.experts, self.top, bias=self.router_b, renormalise=self.renormalise)
-        gate_up = gemm.linear(x, self.gate_up)
+        gate_up = gemm.linear(x, self.gate_up, chain=True)
         inner = mixer_ops.expert_gated_act(gate_up, self.up_at, weights, self.experts, self.inner, self.shared_inner,
                                            self.activation)
         # the float32 result of the last product goes to a norm
-        return gemm.linear(inner, self.down, out_dtype=torch.float32, few_rows_f32=True)
+        return gemm.linear(inner, self.down, out_dtype=torch.float32, few_rows_f32=True, chain=True)

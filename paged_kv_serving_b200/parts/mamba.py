@@ -87,19 +87,19 @@ class Mamba1(Part):
 
     def forward(self, h: torch.Tensor, ctx: StepContext, binding: CacheBinding) -> torch.Tensor:
         starts, slots = ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.STATE_SLOTS)
-        xz = gemm.linear(h, self.in_proj)                                           # [tokens, 2 inner]
+        xz = gemm.linear(h, self.in_proj, chain=True)                                           # [tokens, 2 inner]
         tail = ctx.states[binding.extra[self.TAIL]] if self.taps > 1 else None
         x = mixer_ops.conv_residual(xz[:, :self.inner], self.conv, tail, ctx.ints(ctx.TOKEN_SEQ), starts, slots, self.conv_t,
                                     bias=self.conv_b, residual=False, act="silu")
-        low = gemm.linear(x, self.x_proj, out_dtype=torch.float32, few_rows_f32=True)                  # [tokens, dt_low | B | C]
+        low = gemm.linear(x, self.x_proj, out_dtype=torch.float32, few_rows_f32=True, chain=True)                  # [tokens, dt_low | B | C]
         if ctx.dtype == torch.float32:
             dt_low = low[:, :self.rank_padded]
             dt_pre = gemm.matmul(dt_low, self.dt_proj.t())
         else:
             dt_low = arena.empty((low.shape[0], self.rank_padded), ctx.dtype, low.device)
             dt_low.copy_(low[:, :self.rank_padded])
-            dt_pre = gemm.linear(dt_low, self.dt_proj, out_dtype=torch.float32, few_rows_f32=True)     # [tokens, inner], before bias and softplus
+            dt_pre = gemm.linear(dt_low, self.dt_proj, out_dtype=torch.float32, few_rows_f32=True, chain=True)     # [tokens, inner], before bias and softplus
         y = mixer_ops.selective_scan(x, xz[:, self.inner:], dt_pre, self.dt_b, low, self.b_at, self.c_at, self.A, self.D,
                                      ctx.states[binding.extra[self.STATE]], starts, slots)
         # the float32 result of the last product goes to a norm
-        return gemm.linear(y, self.o, out_dtype=torch.float32, few_rows_f32=True)
+        return gemm.linear(y, self.o, out_dtype=torch.float32, few_rows_f32=True, chain=True)

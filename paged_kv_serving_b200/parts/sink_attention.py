@@ -207,7 +207,7 @@ class SinkWindowAttention(Part):
         group = ctx.groups[binding.group]
         k_pool, v_pool = group.k_pool[binding.index], group.v_pool[binding.index]
         slots = ctx.ints(group.slots_name) if binding.write else None
-        qkv = gemm.linear(x, self.qkv)
+        qkv = gemm.linear(x, self.qkv, chain=True)
         other = None
         if self.value_share == "blend":
             other = ctx.scratch.get(self.share_key)
@@ -233,4 +233,4 @@ class SinkWindowAttention(Part):
             ctx.ints(seq_name), ctx.ints(row_name), self.n_heads, self.n_kv_heads, self.dim, self.vdim, group.page_size,
             self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status)
         # the float32 result of the last product goes to a norm
-        return gemm.linear(attended, self.o, out_dtype=torch.float32, few_rows_f32=True)
+        return gemm.linear(attended, self.o, out_dtype=torch.float32, few_rows_f32=True, chain=True)
