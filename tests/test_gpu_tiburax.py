@@ -338,6 +338,25 @@ def test_greedy_generation_through_the_entry_point(tmp_path, dtype):
                 assert row[token] >= row.max() - 0.1 * row.std(), f"token {place}: far from the plain maximum"
 
 
+def test_forked_samples_share_pages_and_copy_states(tmp_path):
+    """Three greedy samples of one prompt: the prompt is computed once, the samples share its pages
+    (keys and values of different sizes: a private copy of a page is two copies) and each gets a
+    copy of the recurrent states; all three must be the plain greedy continuation."""
+    from paged_kv_serving_b200.api import generate
+    from paged_kv_serving_b200.weights.random_init import write_model_folder
+
+    config = CONFIGS["A"]
+    typed, _ = _specs(config)
+    tensors = random_tensors(config, seed=13, scale=1.5)
+    write_model_folder(tmp_path, typed, tensors)
+    prompt = tokens_for(config, 29, seed=14)
+    got = generate(tmp_path, [prompt], max_new_tokens=9, n=3, dtype="float32", block_size=8, max_batched_tokens=64, max_running_seqs=4)
+    assert len(got[0]) == 3
+    for ids in got[0]:
+        rows = plain_logits(config, tensors, list(prompt) + ids[:-1])[len(prompt) - 1:]
+        assert len(ids) == 9 and all(row[token] >= row.max() - 1e-4 for token, row in zip(ids, rows))
+
+
 def test_command_line_checkpoint_generation_and_trace_program(tmp_path):
     """The design through the command line as a user meets it: a random-weights folder from a
     ``config.json``, greedy generation from it, and ``bin/trace_run`` replaying a trace of it."""
