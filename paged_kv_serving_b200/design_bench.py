@@ -57,8 +57,8 @@ def tiburax_config(size: str) -> dict:
     z = TIBURAX_SIZES[size]
     attention = {"type": "attention", "mixer": {
         "heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
-        "softcap": 50.0, "v_mix": True, "mask": {"size": z["window"], "keep_first": z["keep"]},
-        "rot": {"base": 10000.0, "dims": z["dim"], "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+        "softcap": 30.0, "v_mix": True, "mask": {"size": z["window"], "keep_first": z["keep"]},
+        "rot": {"base": 10000.0, "dims": z["dim"], "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}}
     recurrent = {"type": "mamba1", "mixer": {"inner": z["inner"], "state": z["state"], "dt_rank": z["dt_rank"], "conv": 4}}
     moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]},
            "shared": {"ff": z["shared_ff"]}}

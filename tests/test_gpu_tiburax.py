@@ -655,11 +655,11 @@ def _random_config(rng):
             mixes = bool(rng.random() < 0.6)
             if mixes and share is None:
                 share = (kv, vdim)
-            mixer = _attention(kv * group, kv, dim, vdim, window=int(rng.choice([1, 5, 16, 31, 32, 33, 64, 100, 136, 1000])),
-                               keep=int(rng.choice([0, 0, 1, 4, 6, 16, 17, 70])), rot_dims=rot,
-                               base=float(rng.choice([100.0, 10000.0, 20000.0, 1e6])), scaling=bool(rng.random() < 0.6) and rot > 0,
-                               softcap=float(rng.choice([0.0, 5.0, 30.0, 50.0])), v_mix=mixes,
-                               scale=float(rng.choice([dim ** -0.5, 0.1275, 1.0 / dim, 3.0 * dim ** -0.5])))
+            mixer = _attention(kv * group, kv, dim, vdim, window=int(rng.choice([1, 5, 16, 31, 32, 33, 64, 100, 150, 1000])),
+                               keep=int(rng.choice([0, 0, 1, 4, 7, 16, 17, 70])), rot_dims=rot,
+                               base=float(rng.choice([100.0, 10000.0, 50000.0, 1e6])), scaling=bool(rng.random() < 0.6) and rot > 0,
+                               softcap=float(rng.choice([0.0, 5.0, 30.0, 80.0])), v_mix=mixes,
+                               scale=float(rng.choice([dim ** -0.5, 0.2, 1.0 / dim, 3.0 * dim ** -0.5])))
             if not mixes and rng.random() < 0.5:
                 mixer["mixer"].pop("v_mix")
             if rng.random() < 0.2:
@@ -670,9 +670,9 @@ def _random_config(rng):
         mlp = None
         if rng.random() < 0.8:
             experts = int(rng.choice([1, 2, 4, 8, 12]))
-            mlp = _moe(experts, int(rng.integers(1, experts + 1)), int(rng.choice([8, 12, 32, 96])), int(rng.choice([0, 8, 128, 40])))
+            mlp = _moe(experts, int(rng.integers(1, experts + 1)), int(rng.choice([8, 12, 32, 88])), int(rng.choice([0, 8, 120, 40])))
         layers.append(_layer(mixer, mlp))
-    return _model(layers, vocab=int(rng.choice([50, 97, 576])), width=width, eps=float(rng.choice([1e-6, 1e-5])),
+    return _model(layers, vocab=int(rng.choice([50, 97, 600])), width=width, eps=float(rng.choice([1e-6, 1e-5])),
                   scale=float(rng.choice([1.0, math.sqrt(width), 0.5])))
 
 

@@ -92,7 +92,7 @@ def test_layout_names_roles_and_cache_requests():
 
 @pytest.mark.parametrize("rot", [
     {"base": 10000.0, "dims": 32}, {"base": 500.0, "dims": 6},
-    {"base": 20000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}},
+    {"base": 50000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 24.0, "slow": 2.0}},
     {"base": 100.0, "dims": 16, "scaling": {"factor": 2.0, "original": 64, "fast": 4.0, "slow": 0.5}},
     {"base": 1e6, "dims": 128, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
     {"base": 50.0, "dims": 4, "scaling": {"factor": 1.0, "original": 16, "fast": 1.0, "slow": 1.0}},
