@@ -357,6 +357,32 @@ def test_forked_samples_share_pages_and_copy_states(tmp_path):
         assert len(ids) == 9 and all(row[token] >= row.max() - 1e-4 for token, row in zip(ids, rows))
 
 
+def test_a_cramped_pool_preempts_and_recomputes_states_and_pages():
+    """Four requests in a pool that holds two: requests are preempted, give back pages and state
+    slot, and start again from position 0 in a cleared slot; every request's tokens are still the
+    plain greedy continuation."""
+    from paged_kv_serving_b200.api import engine_for
+    from paged_kv_serving_b200.engine.sequence import Request, SamplingParams
+
+    config = copy.deepcopy(CONFIGS["A"])
+    for layer in config["layers"]:
+        if layer["type"] == "attention":
+            layer["mixer"]["mask"] = {"size": 500, "keep_first": 2}       # nothing leaves the window: pages pile up
+    tensors = random_tensors(config, seed=15, scale=1.5)
+    prompts = [tokens_for(config, n, seed=30 + n) for n in (41, 37, 44, 29)]
+    new = 22
+    engine = engine_for(build(config, tensors, "float32"), prompts, max_new_tokens=new, dtype="float32", block_size=8, num_blocks=20,
+                        max_batched_tokens=48, max_running_seqs=4)
+    for i, prompt in enumerate(prompts):
+        assert engine.submit(Request(request_id=f"r{i}", prompt_token_ids=tuple(prompt), sampling=SamplingParams(max_new_tokens=new))).admitted
+    outputs = {o.request_id: o for o in engine.run_until_idle()}
+    assert engine.scheduler.stats.preemptions > 0, "the cramped pool must preempt"
+    for i, prompt in enumerate(prompts):
+        ids = list(outputs[f"r{i}"].samples[0].token_ids)
+        rows = plain_logits(config, tensors, list(prompt) + ids[:-1])[len(prompt) - 1:]
+        assert len(ids) == new and all(row[token] >= row.max() - 1e-4 for token, row in zip(ids, rows)), f"request {i}"
+
+
 def test_command_line_checkpoint_generation_and_trace_program(tmp_path):
     """The design through the command line as a user meets it: a random-weights folder from a
     ``config.json``, greedy generation from it, and ``bin/trace_run`` replaying a trace of it."""
