@@ -237,6 +237,249 @@ attention_sink_kernel(const A* __restrict__ q, A* __restrict__ out, const C* __r
   }
 }
 
+// --- attention on tensor cores (bfloat16, head sizes that are multiples of 16) -----------------------
+//
+// One block of 4 warps per (64 query rows of one entry, query head); each warp owns 16 rows. Keys
+// and values are walked in tiles of 64 absolute positions, aligned to multiples of 64 from position
+// 0 (first the tiles that hold kept first tokens, then the window's; one range where they meet),
+// double-buffered with cp.async from the pages the block table names. Both products run on
+// mma.sync m16n8k16 (bfloat16 operands, float32 accumulators); scores, cap, mask, maxima, sums and
+// the output accumulator are float32. The key size is a run-time number (it only sets the number
+// of k-steps of the first product); the value size is a template parameter (it sizes the
+// accumulator). Entries of a few rows (decode) take the same kernel: one block per entry and head.
+
+constexpr int SM_BM = 64, SM_BN = 64, SM_THREADS = 128, SM_PAD = 8;
+
+struct SinkMmaParams {
+  const bf16* q;
+  int q_ld;
+  bf16* out;
+  const bf16* k_pool;
+  const bf16* v_pool;
+  const int32_t* block_table;
+  int table_stride;
+  const int32_t* seq_starts;
+  const int32_t* first_pos;
+  const int32_t* work_seq;
+  const int32_t* work_q0;
+  int n_heads, n_kv, dk, page_size, window, keep_first;
+  float scale_log2, cap_log2, cap_x;   // cap c: c log2(e) and 2 scale / c log2(e); 0: no cap
+  int num_pages;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t sm_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void sm_cp16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sm_u32(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void sm_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void sm_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void sm_ldm4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sm_u32(p)));
+}
+__device__ __forceinline__ void sm_ldm4t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(sm_u32(p)));
+}
+__device__ __forceinline__ void sm_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t sm_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// 64 rows of keys or values from absolute position `base` into a padded tile [64][d + 8]. Two
+// threads share a row (its page is looked up once a thread); rows outside what the block's
+// queries can see, and rows whose page was given back, are zero-filled.
+__device__ __forceinline__ void sm_load_tile(bf16* tile, const bf16* pool, const int32_t* table, int base, int key_lo,
+                                             int key_hi, int keep, int kvh, int n_kv, int page_size, int d, int num_pages,
+                                             int* status) {
+  const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
+  const int pos = base + row;
+  const int ld = d + SM_PAD, chunks = d >> 3;
+  bf16* dst = tile + row * ld;
+  int page = -1;
+  if (pos < key_hi && (pos >= key_lo || pos < keep)) page = checked_page(table[pos / page_size], num_pages, status);
+  if (page >= 0) {
+    const bf16* src = pool + (((size_t)page * n_kv + kvh) * page_size + (pos % page_size)) * d;
+    for (int c = half; c < chunks; c += 2) sm_cp16(dst + c * 8, src + c * 8);
+  } else {
+    for (int c = half; c < chunks; c += 2) *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+template <int DV>
+__global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const SinkMmaParams p) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  constexpr int LDV = DV + SM_PAD;
+  constexpr int DTILES = DV / 8;
+  const int dk = p.dk, ldk = dk + SM_PAD, ksteps = dk >> 4;
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  bf16* q_s = reinterpret_cast<bf16*>(sm_raw);        // [64][ldk]
+  bf16* k_s = q_s + SM_BM * ldk;                       // [2][64][ldk]
+  bf16* v_s = k_s + 2 * SM_BN * ldk;                   // [2][64][LDV]
+
+  const int s = p.work_seq[blockIdx.x], q0 = p.work_q0[blockIdx.x];
+  const int head = blockIdx.y;
+  const int kvh = head / (p.n_heads / p.n_kv);
+  const int tok0 = p.seq_starts[s];
+  const int n_q = p.seq_starts[s + 1] - tok0;
+  const int pos0 = p.first_pos[s];
+  const int rows_valid = min(SM_BM, n_q - q0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+
+  const int qpos_first = pos0 + q0;
+  const int key_hi = qpos_first + rows_valid;                                   // exclusive
+  const int key_lo = p.window > 0 ? max(0, qpos_first - p.window + 1) : 0;
+  const int keep = p.window > 0 ? min(p.keep_first, key_hi) : 0;
+  const int tile_end = (key_hi - 1) / SM_BN;
+  int window_tile = key_lo / SM_BN, kept = (keep + SM_BN - 1) / SM_BN;
+  if (kept >= window_tile) {            // the kept tokens' tiles reach the window's: one range
+    if (kept > 0) window_tile = 0;
+    kept = 0;
+  }
+  const int tile_begin = window_tile, kept_tiles = kept;
+  const int n_tiles = kept_tiles + tile_end - tile_begin + 1;
+  auto tile_of = [=](int j) { return j < kept_tiles ? j : tile_begin + (j - kept_tiles); };
+  const int32_t* table = p.block_table + (size_t)s * p.table_stride;
+
+  for (int idx = threadIdx.x; idx < SM_BM * (dk >> 3); idx += SM_THREADS) {
+    const int row = idx / (dk >> 3), chunk = idx - row * (dk >> 3);
+    bf16* dst = q_s + row * ldk + chunk * 8;
+    if (row < rows_valid)
+      sm_cp16(dst, p.q + (size_t)(tok0 + q0 + row) * p.q_ld + (size_t)head * dk + chunk * 8);
+    else
+      *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  sm_load_tile(k_s, p.k_pool, table, tile_of(0) * SM_BN, key_lo, key_hi, keep, kvh, p.n_kv, p.page_size, dk, p.num_pages, p.status);
+  sm_load_tile(v_s, p.v_pool, table, tile_of(0) * SM_BN, key_lo, key_hi, keep, kvh, p.n_kv, p.page_size, DV, p.num_pages, p.status);
+  sm_commit();
+
+  const int row_a = warp * 16 + g, row_b = row_a + 8;
+  const int qpos_a = qpos_first + row_a, qpos_b = qpos_first + row_b;
+  const int warp_qpos_min = qpos_first + warp * 16;
+  const int warp_qpos_max = min(qpos_first + warp * 16 + 15, key_hi - 1);
+  const bool warp_active = warp * 16 < rows_valid;
+
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
+  float o[DTILES][4];
+#pragma unroll
+  for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+
+  for (int j = 0; j < n_tiles; ++j) {
+    const int stage = j & 1;
+    const int base = tile_of(j) * SM_BN;
+    if (j + 1 < n_tiles) {
+      const int next = tile_of(j + 1) * SM_BN;
+      sm_load_tile(k_s + (stage ^ 1) * SM_BN * ldk, p.k_pool, table, next, key_lo, key_hi, keep, kvh, p.n_kv, p.page_size, dk,
+                   p.num_pages, p.status);
+      sm_load_tile(v_s + (stage ^ 1) * SM_BN * LDV, p.v_pool, table, next, key_lo, key_hi, keep, kvh, p.n_kv, p.page_size, DV,
+                   p.num_pages, p.status);
+      sm_commit();
+      sm_wait<1>();
+    } else {
+      sm_wait<0>();
+    }
+    __syncthreads();
+    const bf16* kt = k_s + stage * SM_BN * ldk;
+    const bf16* vt = v_s + stage * SM_BN * LDV;
+
+    // a warp whose rows all sit before this tile, or after its window with no kept token in the tile, has nothing to do
+    const bool skip = !warp_active || base > warp_qpos_max ||
+                      (p.window > 0 && base + SM_BN - 1 < warp_qpos_min - p.window + 1 && base >= keep);
+    if (!skip) {
+      float sc[SM_BN / 8][4];
+#pragma unroll
+      for (int i = 0; i < SM_BN / 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
+      for (int kk = 0; kk < ksteps; ++kk) {
+        uint32_t a[4];
+        sm_ldm4(a, q_s + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldk + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+        for (int jj = 0; jj < SM_BN / 16; ++jj) {
+          uint32_t b[4];
+          sm_ldm4(b, kt + (jj * 16 + (lane & 7) + 8 * (lane >> 4)) * ldk + kk * 16 + 8 * ((lane >> 3) & 1));
+          sm_mma(sc[2 * jj], a, b[0], b[1]);
+          sm_mma(sc[2 * jj + 1], a, b[2], b[3]);
+        }
+      }
+      // scale or cap (to the log2 domain) and mask by absolute position
+      float tmax_a = -INFINITY, tmax_b = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < SM_BN / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = sc[i][e] * p.scale_log2;
+          if (p.cap_log2 > 0.0f) v = p.cap_log2 * (1.0f - 2.0f / (1.0f + exp2f(sc[i][e] * p.cap_x)));
+          const int kpos = base + i * 8 + 2 * t4 + (e & 1);
+          const int qpos = (e < 2) ? qpos_a : qpos_b;
+          const bool ok = kpos <= qpos && (p.window == 0 || kpos > qpos - p.window || kpos < keep);
+          v = ok ? v : -INFINITY;
+          sc[i][e] = v;
+          if (e < 2) tmax_a = fmaxf(tmax_a, v); else tmax_b = fmaxf(tmax_b, v);
+        }
+      }
+      tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 1));
+      tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 2));
+      tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 1));
+      tmax_b = fmaxf(tmax_b, __shfl_xor_sync(0xffffffffu, tmax_b, 2));
+      const float new_a = fmaxf(m_a, tmax_a), new_b = fmaxf(m_b, tmax_b);
+      // a row with nothing visible yet keeps shift 0 so that exp2(-inf - 0) = 0
+      const float shift_a = new_a == -INFINITY ? 0.0f : new_a, shift_b = new_b == -INFINITY ? 0.0f : new_b;
+      const float resc_a = exp2f(m_a - shift_a), resc_b = exp2f(m_b - shift_b);
+      m_a = new_a; m_b = new_b;
+      float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+      for (int i = 0; i < SM_BN / 8; ++i) {
+        sc[i][0] = exp2f(sc[i][0] - shift_a); sc[i][1] = exp2f(sc[i][1] - shift_a);
+        sc[i][2] = exp2f(sc[i][2] - shift_b); sc[i][3] = exp2f(sc[i][3] - shift_b);
+        sum_a += sc[i][0] + sc[i][1];
+        sum_b += sc[i][2] + sc[i][3];
+      }
+      l_a = l_a * resc_a + sum_a;
+      l_b = l_b * resc_b + sum_b;
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i) { o[i][0] *= resc_a; o[i][1] *= resc_a; o[i][2] *= resc_b; o[i][3] *= resc_b; }
+#pragma unroll
+      for (int kk = 0; kk < SM_BN / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = sm_pack(sc[2 * kk][0], sc[2 * kk][1]);
+        a[1] = sm_pack(sc[2 * kk][2], sc[2 * kk][3]);
+        a[2] = sm_pack(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+        a[3] = sm_pack(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+        for (int dd = 0; dd < DTILES / 2; ++dd) {
+          uint32_t b[4];
+          sm_ldm4t(b, vt + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LDV + dd * 16 + 8 * (lane >> 4));
+          sm_mma(o[2 * dd], a, b[0], b[1]);
+          sm_mma(o[2 * dd + 1], a, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  const float inv_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, inv_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
+  const size_t out_stride = (size_t)p.n_heads * DV;
+  if (row_a < rows_valid) {
+    bf16* dst = p.out + (size_t)(tok0 + q0 + row_a) * out_stride + (size_t)head * DV;
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = sm_pack(o[i][0] * inv_a, o[i][1] * inv_a);
+  }
+  if (row_b < rows_valid) {
+    bf16* dst = p.out + (size_t)(tok0 + q0 + row_b) * out_stride + (size_t)head * DV;
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = sm_pack(o[i][2] * inv_b, o[i][3] * inv_b);
+  }
+}
+
 }  // namespace pkv
 
 using namespace pkv;
@@ -316,4 +559,53 @@ PKV_EXPORT int pkv_attention_sink(const void* q, int q_ld, void* out, int act_dt
   if (act_dtype == PKV_BF16 && cache_dtype == PKV_F32) PKV_SINK(bf16, float);
 #undef PKV_SINK
   return PKV_ERR_DTYPE;
+}
+
+template <int DV>
+static int launch_sink_mma(const SinkMmaParams& p, int n_work, cudaStream_t s) {
+  const size_t smem = ((size_t)3 * SM_BM * (p.dk + SM_PAD) + (size_t)2 * SM_BN * (DV + SM_PAD)) * sizeof(bf16);
+  if (smem > 200 * 1024) return PKV_ERR_LIMIT;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attention_sink_mma_kernel<DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return launch_kernel(attention_sink_mma_kernel<DV>, dim3(n_work, p.n_heads), dim3(SM_THREADS), smem, s, true, 0, p);
+}
+
+// 1 when the tensor-core kernel takes these sizes (bfloat16 only): key and value sizes that are
+// multiples of 16, values of at most 128, keys of at most 256, query rows on 16-byte boundaries.
+PKV_EXPORT int pkv_attention_sink_mma_supports(int dk, int dv, int q_ld) {
+  return (dk >= 16 && dk <= 256 && dk % 16 == 0 && dv >= 16 && dv <= 128 && dv % 16 == 0 && q_ld % 8 == 0) ? 1 : 0;
+}
+
+PKV_EXPORT int pkv_attention_sink_mma_rows() { return SM_BM; }
+
+// The work list is in blocks of 64 query rows of an entry (work_q0: the block's first query).
+PKV_EXPORT int pkv_attention_sink_mma(const void* q, int q_ld, void* out, const void* k_pool, const void* v_pool,
+                                      const int32_t* block_table, int table_stride, const int32_t* seq_starts,
+                                      const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_q0, int n_work,
+                                      int n_heads, int n_kv, int dk, int dv, int page_size, int window, int keep_first,
+                                      float scale, float softcap, int num_pages, int* status, void* stream) {
+  if (n_work <= 0) return 0;
+  if (!pkv_attention_sink_mma_supports(dk, dv, q_ld)) return PKV_ERR_LIMIT;
+  if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size <= 0 || window < 0 || keep_first < 0 || num_pages <= 0 ||
+      softcap < 0.0f || !(scale > 0.0f) || n_heads > 65535)
+    return PKV_ERR_SIZE;
+  if ((uintptr_t)q % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 4) return PKV_ERR_ALIGN;
+  const float log2e = 1.4426950408889634f;
+  SinkMmaParams p{(const bf16*)q, q_ld, (bf16*)out, (const bf16*)k_pool, (const bf16*)v_pool, block_table, table_stride,
+                  seq_starts, first_pos, work_seq, work_q0, n_heads, n_kv, dk, page_size, window, keep_first, scale * log2e,
+                  softcap * log2e, softcap > 0.0f ? 2.0f * scale / softcap * log2e : 0.0f, num_pages, status};
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (dv) {
+    case 16: return launch_sink_mma<16>(p, n_work, s);
+    case 32: return launch_sink_mma<32>(p, n_work, s);
+    case 48: return launch_sink_mma<48>(p, n_work, s);
+    case 64: return launch_sink_mma<64>(p, n_work, s);
+    case 80: return launch_sink_mma<80>(p, n_work, s);
+    case 96: return launch_sink_mma<96>(p, n_work, s);
+    case 112: return launch_sink_mma<112>(p, n_work, s);
+    case 128: return launch_sink_mma<128>(p, n_work, s);
+  }
+  return PKV_ERR_LIMIT;
 }

@@ -19,7 +19,7 @@ from paged_kv_serving_b200.ops.arena import empty as _empty
 __all__ = ["ACTIVATIONS", "act_times_table", "bias_act", "conv_residual", "expert_act", "expert_gated_act", "norm_residual", "latent_attention",
            "latent_attention_mma", "latent_mma_rows_per_block", "latent_mma_supports", "latent_prepare",
            "latent_rows_per_block", "mlstm", "residual_add", "route_top", "token_side", "attention_sink",
-           "attention_sink_rows_per_block", "qkv_prepare", "selective_scan"]
+           "attention_sink_mma", "attention_sink_mma_rows", "attention_sink_mma_supports", "attention_sink_rows_per_block", "qkv_prepare", "selective_scan"]
 
 #: activation names of ``bias_act`` / ``act_times_table`` / ``expert_act``
 ACTIVATIONS = {"none": 0, "gelu_erf": 1, "gelu_tanh": 2, "relu_squared": 3, "sigmoid": 4, "silu": 5}
@@ -492,4 +492,43 @@ def attention_sink(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
               _ptr(block_table), block_table.shape[1], _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), _ptr(work_row0),
               work_seq.numel(), n_heads, n_kv, dim, vdim, page_size, int(window), int(keep_first), float(scale), float(softcap),
               num_pages, _ptr(status), _stream()), "attention_sink")
+    return out
+
+
+def attention_sink_mma_supports(dim: int, vdim: int, q_row_stride: int) -> bool:
+    """Whether the tensor-core form of ``attention_sink`` takes these sizes (bfloat16 only): key
+    and value sizes that are multiples of 16 (keys up to 256, values up to 128)."""
+    if dim % 16 or vdim % 16 or not 16 <= dim <= 256 or not 16 <= vdim <= 128 or q_row_stride % 8:
+        return False     # known without building the library
+    return True
+
+
+def attention_sink_mma_rows() -> int:
+    """Query rows of one work item of ``attention_sink_mma``."""
+    return 64
+
+
+def attention_sink_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                       seq_starts: torch.Tensor, first_pos: torch.Tensor, work_seq: torch.Tensor, work_q0: torch.Tensor,
+                       n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int, window: int, keep_first: int, scale: float,
+                       softcap: float, status: torch.Tensor) -> torch.Tensor:
+    """``attention_sink`` on the tensor cores (``mma.sync``, bfloat16 operands, float32 scores and
+    accumulators) for head sizes that are multiples of 16. The work list is in blocks of
+    ``attention_sink_mma_rows()`` queries of an entry (``work_q0``: the block's first query)."""
+    _need(q, torch.bfloat16, "q"); _need(k_pool, torch.bfloat16, "k_pool"); _need(v_pool, torch.bfloat16, "v_pool")
+    for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
+                    ("work_seq", work_seq), ("work_q0", work_q0)):
+        _need(t, torch.int32, name)
+    tokens = q.shape[0]
+    if q.shape[1] < n_heads * dim:
+        raise ValueError("q is narrower than its heads")
+    out = _empty((tokens, n_heads * vdim), q.dtype, q.device)
+    num_pages = k_pool.numel() // (n_kv * page_size * dim)
+    fn = _fn("attention_sink", "pkv_attention_sink_mma",
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(q), q.shape[1], _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+              _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), _ptr(work_q0), work_seq.numel(), n_heads, n_kv, dim, vdim,
+              page_size, int(window), int(keep_first), float(scale), float(softcap), num_pages, _ptr(status), _stream()),
+           "attention_sink_mma")
     return out

@@ -44,8 +44,10 @@ class SinkWindowAttention(Part):
     for the attention itself, in bfloat16 with keys and values of one size of 64 or 128 and pages
     of a multiple of 8 keys, the tensor-core kernels of ``PagedAttention`` (tcgen05 for runs of
     queries, the TMA-fed split-key kernel for entries of a few rows), which take the kept first
-    tokens as further tiles in front of the window's and cap the scores in their softmax; for
-    every other size and for float32 the general kernel ``ops.mixer_ops.attention_sink``.
+    tokens as further tiles in front of the window's and cap the scores in their softmax; in
+    bfloat16 with other head sizes that are multiples of 16 (keys and values may differ) the
+    ``mma.sync`` kernel ``ops.mixer_ops.attention_sink_mma``; for every other size and for float32
+    the general kernel ``ops.mixer_ops.attention_sink``.
     """
 
     graph_safe = True
@@ -115,6 +117,9 @@ class SinkWindowAttention(Part):
         if self._fast(ctx, ctx.groups[binding.group].page_size):
             self._plan_fast(ctx, ctx.groups[binding.group].page_size)
             return
+        if self._mma(ctx):
+            self._plan_mma(ctx)
+            return
         seq_name, row_name = self._work_names()
         if seq_name in ctx.arena:
             return
@@ -136,6 +141,26 @@ class SinkWindowAttention(Part):
             self._fast_ok[key] = (ops.attention_tcgen05_supports(self.dim, page_size, self.fused_rows)
                                   and ops.attention_decode_tma_supports(self.dim, page_size, self.fused_rows))
         return self._fast_ok[key]
+
+    def _mma(self, ctx: StepContext) -> bool:
+        """Whether the ``mma.sync`` kernel serves this mixer in this step (when ``_fast`` does not)."""
+        return (self.USE_TENSOR_CORES and ctx.dtype == torch.bfloat16
+                and mixer_ops.attention_sink_mma_supports(self.dim, self.vdim, self.fused_rows))
+
+    def _plan_mma(self, ctx: StepContext) -> None:
+        seq_name, q0_name = "sink_attention/mma/work_seq", "sink_attention/mma/work_q0"
+        if seq_name in ctx.arena:
+            return
+        rows = mixer_ops.attention_sink_mma_rows()
+        lens = np.asarray(ctx.seq_lens, dtype=np.int64)
+        first = np.asarray(ctx.first_positions, dtype=np.int64)
+        blocks = (lens + rows - 1) // rows
+        work_seq = np.repeat(np.arange(len(lens), dtype=np.int64), blocks)
+        starts = np.cumsum(blocks) - blocks
+        work_q0 = (np.arange(int(blocks.sum()), dtype=np.int64) - np.repeat(starts, blocks)) * rows
+        order = np.argsort(-(first[work_seq] + work_q0), kind="stable")       # the longest key ranges first
+        ctx.arena.add(seq_name, work_seq[order])
+        ctx.arena.add(q0_name, work_q0[order])
 
     def _fast_key(self, page_size: int) -> str:
         return (f"sink_attention/fast/h{self.n_heads}k{self.n_kv_heads}d{self.dim}w{self.window or 0}s{self.keep_first}"
@@ -227,6 +252,12 @@ class SinkWindowAttention(Part):
             v_other=other, blend=self.blend if other is not None else None, keep_values=shared)
         if self._fast(ctx, group.page_size):
             return gemm.linear(self._attend_fast(qkv, ctx, group, k_pool, v_pool), self.o, out_dtype=torch.float32, few_rows_f32=True)
+        if self._mma(ctx):
+            attended = mixer_ops.attention_sink_mma(
+                qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
+                ctx.ints("sink_attention/mma/work_seq"), ctx.ints("sink_attention/mma/work_q0"), self.n_heads, self.n_kv_heads,
+                self.dim, self.vdim, group.page_size, self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status)
+            return gemm.linear(attended, self.o, out_dtype=torch.float32, few_rows_f32=True, chain=True)
         seq_name, row_name = self._work_names()
         attended = mixer_ops.attention_sink(
             qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),

@@ -658,6 +658,55 @@ def test_tensor_core_attention_with_window_kept_tokens_and_cap(what):
         assert float(np.median(error)) <= 0.03 and float(error.max()) <= 0.15, f"{what}, {name}: rows off by up to {error.max():.3e}"
 
 
+def _sharp_two_sizes(dim, vdim, heads, kv_heads, window, keep, softcap, rot_dims):
+    return _attention(heads, kv_heads, dim, vdim, window=window, keep=keep, rot_dims=rot_dims, softcap=softcap,
+                      scale=4.0 * dim ** -0.5, v_mix=False)
+
+
+MMA = {
+    "keys_of_96_values_of_48": (_sharp_two_sizes(96, 48, 4, 2, 70, 5, 30.0, 32), 8),
+    "keys_of_16_values_of_128": (_sharp_two_sizes(16, 128, 2, 1, 150, 66, 50.0, 16), 16),
+    "keys_of_160_values_of_16_on_tile_borders": (_sharp_two_sizes(160, 16, 2, 1, 128, 64, 20.0, 64), 16),
+    "keys_of_48_values_of_80_no_cap": (_sharp_two_sizes(48, 80, 3, 3, 100, 40, 0.0, 16), 4),
+    "keys_of_256_no_window": (_sharp_two_sizes(256, 32, 2, 2, 100000, 0, 3.0, 64), 32),
+    "window_of_three_many_heads_a_key": (_sharp_two_sizes(32, 112, 8, 1, 3, 1, 30.0, 32), 8),
+}
+
+
+@pytest.mark.parametrize("what", sorted(MMA))
+def test_mma_attention_for_head_sizes_in_steps_of_16(what):
+    from paged_kv_serving_b200.parts import SinkWindowAttention
+
+    mixer, page = MMA[what]
+    config = _model([_layer(mixer, None), _layer(copy.deepcopy(mixer), None)], vocab=120, width=64, scale=2.0)
+    config["layers"][0]["mixer"]["v_mix"] = config["layers"][1]["mixer"]["v_mix"] = True
+    tensors = random_tensors(config, seed=71, scale=1.5)
+    tokens = tokens_for(config, 330, seed=72)
+    want = plain_logits(config, tensors, tokens)
+
+    def run(tensor_cores):
+        before = SinkWindowAttention.USE_TENSOR_CORES
+        SinkWindowAttention.USE_TENSOR_CORES = tensor_cores
+        try:
+            session = session_for(config, tensors, "bfloat16", max_tokens=384, page=page)
+            probe = type("C", (), {"dtype": torch.bfloat16})()
+            assert not session.model.layout.blocks[0].mixer._fast(probe, page)
+            assert session.model.layout.blocks[0].mixer._mma(probe) == tensor_cores
+            rows = [session.step([{"id": "r", "tokens": tokens[:200], "want": list(range(200))}]),
+                    session.step([{"id": "r", "tokens": tokens[200:240], "want": list(range(40))}]),
+                    session.step([{"id": "r", "tokens": tokens[240:243], "want": [0, 1, 2]}])]
+            rows += [session.step([{"id": "r", "tokens": [t], "want": [0]}]) for t in tokens[243:]]
+            return np.concatenate(rows)
+        finally:
+            SinkWindowAttention.USE_TENSOR_CORES = before
+
+    for name, got in (("tensor cores", run(True)), ("general kernel", run(False))):
+        gap = got - want
+        gap = gap - gap.mean(axis=-1, keepdims=True)
+        error = np.sqrt((gap ** 2).mean(axis=-1)) / want.std()
+        assert float(np.median(error)) <= 0.03 and float(error.max()) <= 0.15, f"{what}, {name}: rows off by up to {error.max():.3e}"
+
+
 # --- seeded random configurations ------------------------------------------------------------------
 
 
