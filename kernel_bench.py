@@ -5,7 +5,7 @@ rotates over 32 layers' worth of buffers (so that weights, keys and values come 
 a real step) and reports microseconds per launch with the achieved bandwidth or arithmetic rate.
 The sizes come from a preset of ``config/presets.py``; nothing here is used by the engine.
 
-    python kernel_bench.py [gemm] [decode-gemm] [prefill-attention] [decode-attention] [elementwise] [scan]
+    python kernel_bench.py [gemm] [decode-gemm] [prefill-attention] [decode-attention] [elementwise] [scan] [sink-attention]
 """
 
 from __future__ import annotations
@@ -226,9 +226,75 @@ def bench_scan(config, page: int) -> None:
               f"{tokens * inner * n_state / us / 1e3:6.1f} G state updates/s")
 
 
+def bench_sink_attention(config, page: int) -> None:
+    """Attention over a window of 1,024 keys with 4 kept first tokens and a score cap, 16 query and 4 key/value
+    heads: heads of 128 (tcgen05 for a prompt, the TMA-fed kernel for decode entries), and keys of 96 with values
+    of 48 (the mma.sync kernel and the general one). One prompt of 2,048 tokens; 8 decode entries at 1,024 keys."""
+    from paged_kv_serving_b200.ops import mixer_ops
+
+    h, kv, window, keep, cap = 16, 4, 1024, 4, 30.0
+    status = ops.status_word("cuda")
+
+    def lists(queries, batch, rows):
+        blocks = -(-queries // rows)
+        seq = torch.tensor([s for q in reversed(range(blocks)) for s in range(batch)], dtype=torch.int32, device="cuda")
+        q0 = torch.tensor([q * rows for q in reversed(range(blocks)) for s in range(batch)], dtype=torch.int32, device="cuda")
+        return seq, q0
+
+    for dk, dv in ((128, 128), (96, 48)):
+        for batch, context, queries in ((1, 2048, 2048), (8, 1024, 1)):
+            pages_per = -(-context // page)
+            pages = batch * pages_per
+            layers = 8
+            k = torch.randn((layers, pages, kv, page, dk), device="cuda", dtype=torch.bfloat16)
+            v = torch.randn((layers, pages, kv, page, dv), device="cuda", dtype=torch.bfloat16)
+            table = torch.tensor([[j * batch + i for j in range(pages_per)] for i in range(batch)], dtype=torch.int32, device="cuda")
+            tokens = batch * queries
+            qkv = torch.randn((tokens, h * dk + kv * (dk + dv)), device="cuda", dtype=torch.bfloat16)
+            out = torch.empty((tokens, h * dv), device="cuda", dtype=torch.bfloat16)
+            starts = torch.arange(0, tokens + 1, queries, dtype=torch.int32, device="cuda")
+            first = torch.full((batch,), context - queries, dtype=torch.int32, device="cuda")
+            if queries > 1:
+                pairs = window * (window + 1) / 2 + (queries - window) * (window + keep)
+            else:
+                pairs = batch * (window + keep)
+            flops = 2.0 * h * (dk + dv) * pairs
+            cache_bytes = (batch * (window + keep) if queries == 1 else context) * kv * (dk + dv) * 2
+            scale = 1 / math.sqrt(dk)
+            forms = []
+            if dk == dv:
+                if queries > 1:
+                    seq, q0 = lists(queries, batch, ops.attention_tcgen05_rows())
+                    forms.append(("tcgen05", lambda i: ops.attention_prefill_tcgen05(
+                        qkv, out, k[i % layers], v[i % layers], table, starts, first, seq, q0, h, kv, dk, page, window, scale, status,
+                        keep_first=keep, softcap=cap)))
+                else:
+                    entries = torch.arange(batch, dtype=torch.int32, device="cuda")
+                    forms.append(("TMA decode", lambda i: ops.attention_decode_tma(
+                        qkv, out, k[i % layers], v[i % layers], table, starts, first, entries, 1, h, kv, dk, page, window, scale, 8,
+                        status, False, keep_first=keep, softcap=cap)))
+            seq, q0 = lists(queries, batch, mixer_ops.attention_sink_mma_rows())
+            splits = 1 if queries > 1 else 4
+            forms.append(("mma.sync", lambda i: mixer_ops.attention_sink_mma(
+                qkv, k[i % layers], v[i % layers], table, starts, first, seq, q0, h, kv, dk, dv, page, window, keep, scale, cap, status,
+                num_splits=splits)))
+            rows = mixer_ops.attention_sink_rows_per_block()
+            group_rows = queries * (h // kv)
+            blocks = -(-group_rows // rows)
+            gseq = torch.tensor([s for s in range(batch) for _ in range(blocks)], dtype=torch.int32, device="cuda")
+            grow = torch.tensor([b * rows for s in range(batch) for b in range(blocks)], dtype=torch.int32, device="cuda")
+            forms.append(("general", lambda i: mixer_ops.attention_sink(
+                qkv, k[i % layers], v[i % layers], table, starts, first, gseq, grow, h, kv, dk, dv, page, window, keep, scale, cap, status)))
+            for name, fn in forms:
+                us = timed(fn, launches=8)
+                print(f"sink attention keys {dk:3d} values {dv:3d} {name:10s} {batch} x {queries:4d} queries, {context} keys: {us:8.1f} us "
+                      f"{flops / us / 1e6:7.1f} TFLOP/s {cache_bytes / us / 1e6:5.2f} TB/s of cache")
+    assert int(status.item()) == 0
+
+
 def main() -> int:
     cases = {"gemm": None, "decode-gemm": None, "prefill-attention": bench_prefill_attention, "decode-attention": bench_decode_attention,
-             "elementwise": bench_elementwise, "scan": bench_scan}
+             "elementwise": bench_elementwise, "scan": bench_scan, "sink-attention": bench_sink_attention}
     parser = argparse.ArgumentParser(description=__doc__.splitlines()[0])
     parser.add_argument("cases", nargs="*", choices=[*cases, []], help="which kernels to time (default: all)")
     parser.add_argument("--preset", default="llama-3-8b")

@@ -246,7 +246,9 @@ attention_sink_kernel(const A* __restrict__ q, A* __restrict__ out, const C* __r
 // mma.sync m16n8k16 (bfloat16 operands, float32 accumulators); scores, cap, mask, maxima, sums and
 // the output accumulator are float32. The key size is a run-time number (it only sets the number
 // of k-steps of the first product); the value size is a template parameter (it sizes the
-// accumulator). Entries of a few rows (decode) take the same kernel: one block per entry and head.
+// accumulator). Entries of a few rows (decode) take the same kernel, one block per entry and head;
+// for steps that hold nothing else the tile list of every block is cut into up to 8 shares that run
+// side by side (blockIdx.z) and a second kernel merges their (maximum, sum, accumulator) states.
 
 constexpr int SM_BM = 64, SM_BN = 64, SM_THREADS = 128, SM_PAD = 8;
 
@@ -266,6 +268,9 @@ struct SinkMmaParams {
   float scale_log2, cap_log2, cap_x;   // cap c: c log2(e) and 2 scale / c log2(e); 0: no cap
   int num_pages;
   int* status;
+  int num_splits;                      // > 1: blockIdx.z takes a share of the tile list and leaves its state in scratch
+  float* part_o;                       // [T * H, splits, DV] unnormalised sums
+  float* part_ml;                      // [T * H, splits, 2] maximum (log2 domain) and sum of weights
 };
 
 __device__ __forceinline__ uint32_t sm_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -345,9 +350,21 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
     kept = 0;
   }
   const int tile_begin = window_tile, kept_tiles = kept;
-  const int n_tiles = kept_tiles + tile_end - tile_begin + 1;
+  const int listed = kept_tiles + tile_end - tile_begin + 1;
   auto tile_of = [=](int j) { return j < kept_tiles ? j : tile_begin + (j - kept_tiles); };
   const int32_t* table = p.block_table + (size_t)s * p.table_stride;
+  // this block's share of the tile list
+  const int per_split = (listed + p.num_splits - 1) / p.num_splits;
+  const int j_begin = blockIdx.z * per_split, j_end = min(listed, j_begin + per_split);
+  if (j_begin >= j_end) {               // (only with splits) nothing to do: an empty state
+    for (int idx = threadIdx.x; idx < rows_valid; idx += SM_THREADS) {
+      const size_t at = ((size_t)(tok0 + q0 + idx) * p.n_heads + head) * p.num_splits + blockIdx.z;
+      p.part_ml[2 * at] = -INFINITY;
+      p.part_ml[2 * at + 1] = 0.0f;
+      for (int d = 0; d < DV; ++d) p.part_o[at * DV + d] = 0.0f;
+    }
+    return;
+  }
 
   for (int idx = threadIdx.x; idx < SM_BM * (dk >> 3); idx += SM_THREADS) {
     const int row = idx / (dk >> 3), chunk = idx - row * (dk >> 3);
@@ -357,8 +374,8 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
     else
       *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
   }
-  sm_load_tile(k_s, p.k_pool, table, tile_of(0) * SM_BN, key_lo, key_hi, keep, kvh, p.n_kv, p.page_size, dk, p.num_pages, p.status);
-  sm_load_tile(v_s, p.v_pool, table, tile_of(0) * SM_BN, key_lo, key_hi, keep, kvh, p.n_kv, p.page_size, DV, p.num_pages, p.status);
+  sm_load_tile(k_s, p.k_pool, table, tile_of(j_begin) * SM_BN, key_lo, key_hi, keep, kvh, p.n_kv, p.page_size, dk, p.num_pages, p.status);
+  sm_load_tile(v_s, p.v_pool, table, tile_of(j_begin) * SM_BN, key_lo, key_hi, keep, kvh, p.n_kv, p.page_size, DV, p.num_pages, p.status);
   sm_commit();
 
   const int row_a = warp * 16 + g, row_b = row_a + 8;
@@ -372,10 +389,10 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
 #pragma unroll
   for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
 
-  for (int j = 0; j < n_tiles; ++j) {
-    const int stage = j & 1;
+  for (int j = j_begin; j < j_end; ++j) {
+    const int stage = (j - j_begin) & 1;
     const int base = tile_of(j) * SM_BN;
-    if (j + 1 < n_tiles) {
+    if (j + 1 < j_end) {
       const int next = tile_of(j + 1) * SM_BN;
       sm_load_tile(k_s + (stage ^ 1) * SM_BN * ldk, p.k_pool, table, next, key_lo, key_hi, keep, kvh, p.n_kv, p.page_size, dk,
                    p.num_pages, p.status);
@@ -466,6 +483,22 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
 
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  if (p.num_splits > 1) {
+    // this share's state: the merge kernel folds the shares of a row in ascending order
+    if (row_a < rows_valid) {
+      const size_t at = ((size_t)(tok0 + q0 + row_a) * p.n_heads + head) * p.num_splits + blockIdx.z;
+      if (t4 == 0) { p.part_ml[2 * at] = m_a; p.part_ml[2 * at + 1] = l_a; }
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i) { p.part_o[at * DV + i * 8 + 2 * t4] = o[i][0]; p.part_o[at * DV + i * 8 + 2 * t4 + 1] = o[i][1]; }
+    }
+    if (row_b < rows_valid) {
+      const size_t at = ((size_t)(tok0 + q0 + row_b) * p.n_heads + head) * p.num_splits + blockIdx.z;
+      if (t4 == 0) { p.part_ml[2 * at] = m_b; p.part_ml[2 * at + 1] = l_b; }
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i) { p.part_o[at * DV + i * 8 + 2 * t4] = o[i][2]; p.part_o[at * DV + i * 8 + 2 * t4 + 1] = o[i][3]; }
+    }
+    return;
+  }
   const float inv_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, inv_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
   const size_t out_stride = (size_t)p.n_heads * DV;
   if (row_a < rows_valid) {
@@ -478,6 +511,28 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
 #pragma unroll
     for (int i = 0; i < DTILES; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = sm_pack(o[i][2] * inv_b, o[i][3] * inv_b);
   }
+}
+
+// out[row, d] = sum_z o_z 2^(m_z - M) / sum_z l_z 2^(m_z - M) over the shares z of a row, M their largest maximum.
+__global__ void sink_mma_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
+                                      long long rows, int dv, int splits) {
+  dependents_may_launch();
+  wait_for_prior_kernels();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * dv) return;
+  const long long row = i / dv;
+  const int d = (int)(i - row * dv);
+  float m = -INFINITY;
+  for (int z = 0; z < splits; ++z) m = fmaxf(m, part_ml[2 * (row * splits + z)]);
+  float l = 0.0f, acc = 0.0f;
+  if (m > -INFINITY) {
+    for (int z = 0; z < splits; ++z) {
+      const float f = exp2f(part_ml[2 * (row * splits + z)] - m);
+      l += part_ml[2 * (row * splits + z) + 1] * f;
+      acc += part_o[(row * splits + z) * dv + d] * f;
+    }
+  }
+  out[i] = from_float<bf16>(l > 0.0f ? acc / l : 0.0f);
 }
 
 }  // namespace pkv
@@ -569,7 +624,9 @@ static int launch_sink_mma(const SinkMmaParams& p, int n_work, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(attention_sink_mma_kernel<DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return launch_kernel(attention_sink_mma_kernel<DV>, dim3(n_work, p.n_heads), dim3(SM_THREADS), smem, s, true, 0, p);
+  const int rc = launch_kernel(attention_sink_mma_kernel<DV>, dim3(n_work, p.n_heads, p.num_splits), dim3(SM_THREADS), smem, s,
+                               true, 0, p);
+  return rc;
 }
 
 // 1 when the tensor-core kernel takes these sizes (bfloat16 only): key and value sizes that are
@@ -585,9 +642,11 @@ PKV_EXPORT int pkv_attention_sink_mma(const void* q, int q_ld, void* out, const 
                                       const int32_t* block_table, int table_stride, const int32_t* seq_starts,
                                       const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_q0, int n_work,
                                       int n_heads, int n_kv, int dk, int dv, int page_size, int window, int keep_first,
-                                      float scale, float softcap, int num_pages, int* status, void* stream) {
+                                      float scale, float softcap, int num_pages, int* status, int num_splits, float* part_o,
+                                      float* part_ml, long long tokens, void* stream) {
   if (n_work <= 0) return 0;
   if (!pkv_attention_sink_mma_supports(dk, dv, q_ld)) return PKV_ERR_LIMIT;
+  if (num_splits < 1 || num_splits > 8 || (num_splits > 1 && (!part_o || !part_ml))) return PKV_ERR_SIZE;
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size <= 0 || window < 0 || keep_first < 0 || num_pages <= 0 ||
       softcap < 0.0f || !(scale > 0.0f) || n_heads > 65535)
     return PKV_ERR_SIZE;
@@ -595,17 +654,22 @@ PKV_EXPORT int pkv_attention_sink_mma(const void* q, int q_ld, void* out, const 
   const float log2e = 1.4426950408889634f;
   SinkMmaParams p{(const bf16*)q, q_ld, (bf16*)out, (const bf16*)k_pool, (const bf16*)v_pool, block_table, table_stride,
                   seq_starts, first_pos, work_seq, work_q0, n_heads, n_kv, dk, page_size, window, keep_first, scale * log2e,
-                  softcap * log2e, softcap > 0.0f ? 2.0f * scale / softcap * log2e : 0.0f, num_pages, status};
+                  softcap * log2e, softcap > 0.0f ? 2.0f * scale / softcap * log2e : 0.0f, num_pages, status, num_splits, part_o,
+                  part_ml};
   cudaStream_t s = (cudaStream_t)stream;
+  int rc = PKV_ERR_LIMIT;
   switch (dv) {
-    case 16: return launch_sink_mma<16>(p, n_work, s);
-    case 32: return launch_sink_mma<32>(p, n_work, s);
-    case 48: return launch_sink_mma<48>(p, n_work, s);
-    case 64: return launch_sink_mma<64>(p, n_work, s);
-    case 80: return launch_sink_mma<80>(p, n_work, s);
-    case 96: return launch_sink_mma<96>(p, n_work, s);
-    case 112: return launch_sink_mma<112>(p, n_work, s);
-    case 128: return launch_sink_mma<128>(p, n_work, s);
+    case 16: rc = launch_sink_mma<16>(p, n_work, s); break;
+    case 32: rc = launch_sink_mma<32>(p, n_work, s); break;
+    case 48: rc = launch_sink_mma<48>(p, n_work, s); break;
+    case 64: rc = launch_sink_mma<64>(p, n_work, s); break;
+    case 80: rc = launch_sink_mma<80>(p, n_work, s); break;
+    case 96: rc = launch_sink_mma<96>(p, n_work, s); break;
+    case 112: rc = launch_sink_mma<112>(p, n_work, s); break;
+    case 128: rc = launch_sink_mma<128>(p, n_work, s); break;
   }
-  return PKV_ERR_LIMIT;
+  if (rc != 0 || num_splits == 1) return rc;
+  const long long rows = tokens * n_heads;
+  return launch_kernel(sink_mma_merge_kernel, dim3((unsigned)((rows * dv + 255) / 256)), dim3(256), 0, s, true, 0,
+                       (const float*)part_o, (const float*)part_ml, (bf16*)out, rows, dv, num_splits);
 }

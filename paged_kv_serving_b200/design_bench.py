@@ -121,7 +121,7 @@ class _KernelTimes:
             self._wrap(ops, name, "kernel")
         for name in ("bias_act", "residual_add", "act_times_table", "route_top", "expert_act", "conv_residual", "mlstm",
                      "latent_prepare", "latent_attention", "latent_attention_mma", "norm_residual", "expert_gated_act",
-                     "qkv_prepare", "attention_sink", "selective_scan"):
+                     "qkv_prepare", "attention_sink", "attention_sink_mma", "selective_scan"):
             self._wrap(mixer_ops, name, "kernel")
         self._wrap(gemm, "matmul", "product")
         self._wrap(torch, "bmm", "product")
@@ -234,7 +234,7 @@ def measure(config: dict, peaks: dict, *, prefill_tokens: int = 2048, batch: int
         moved = x.numel() * (2 * x.element_size() + 4) + out.numel() * out.element_size()
         return moved, 0.0
 
-    cost.update({"attention_sink": sink_cost, "selective_scan": scan_cost})
+    cost.update({"attention_sink": sink_cost, "attention_sink_mma": sink_cost, "selective_scan": scan_cost})
     cost.update({"latent_attention": latent_cost, "latent_attention_mma": latent_cost,
                  "attention_prefill_tcgen05": llama_prefill_cost, "attention_prefill_bf16": llama_prefill_cost,
                  "attention_decode_tma": llama_decode_cost, "attention_decode_flat": llama_decode_cost,

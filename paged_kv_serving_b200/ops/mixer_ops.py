@@ -511,10 +511,13 @@ def attention_sink_mma_rows() -> int:
 def attention_sink_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
                        seq_starts: torch.Tensor, first_pos: torch.Tensor, work_seq: torch.Tensor, work_q0: torch.Tensor,
                        n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int, window: int, keep_first: int, scale: float,
-                       softcap: float, status: torch.Tensor) -> torch.Tensor:
+                       softcap: float, status: torch.Tensor, num_splits: int = 1) -> torch.Tensor:
     """``attention_sink`` on the tensor cores (``mma.sync``, bfloat16 operands, float32 scores and
     accumulators) for head sizes that are multiples of 16. The work list is in blocks of
-    ``attention_sink_mma_rows()`` queries of an entry (``work_q0``: the block's first query)."""
+    ``attention_sink_mma_rows()`` queries of an entry (``work_q0``: the block's first query) and
+    must cover every token of the step when ``num_splits`` > 1: every block's key range is then
+    cut into that many shares (at most 8) that run side by side and are merged by a second
+    kernel (for steps of few rows over long contexts)."""
     _need(q, torch.bfloat16, "q"); _need(k_pool, torch.bfloat16, "k_pool"); _need(v_pool, torch.bfloat16, "v_pool")
     for name, t in (("block_table", block_table), ("seq_starts", seq_starts), ("first_pos", first_pos),
                     ("work_seq", work_seq), ("work_q0", work_q0)):
@@ -524,11 +527,18 @@ def attention_sink_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
         raise ValueError("q is narrower than its heads")
     out = _empty((tokens, n_heads * vdim), q.dtype, q.device)
     num_pages = k_pool.numel() // (n_kv * page_size * dim)
+    part_o = part_ml = None
+    if num_splits > 1:
+        part_o = _empty((tokens * n_heads * num_splits, vdim), torch.float32, q.device)
+        part_ml = _empty((tokens * n_heads * num_splits, 2), torch.float32, q.device)
     fn = _fn("attention_sink", "pkv_attention_sink_mma",
              [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_longlong, c_void_p])
     _check(fn(_ptr(q), q.shape[1], _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
               _ptr(seq_starts), _ptr(first_pos), _ptr(work_seq), _ptr(work_q0), work_seq.numel(), n_heads, n_kv, dim, vdim,
-              page_size, int(window), int(keep_first), float(scale), float(softcap), num_pages, _ptr(status), _stream()),
-           "attention_sink_mma")
+              page_size, int(window), int(keep_first), float(scale), float(softcap), num_pages, _ptr(status), int(num_splits),
+              _ptr(part_o), _ptr(part_ml), tokens, _stream()), "attention_sink_mma")
+    if num_splits > 1:
+        ops.LAUNCHES["count"] += 1
     return out

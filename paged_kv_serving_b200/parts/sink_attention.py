@@ -147,8 +147,31 @@ class SinkWindowAttention(Part):
         return (self.USE_TENSOR_CORES and ctx.dtype == torch.bfloat16
                 and mixer_ops.attention_sink_mma_supports(self.dim, self.vdim, self.fused_rows))
 
+    def _mma_splits(self, ctx: StepContext) -> int:
+        """Shares of the key range per block of the ``mma.sync`` kernel: one, unless the step holds
+        only entries of a few tokens over long contexts (decode steps), whose few blocks would
+        each walk their tiles in a row; then as many as still run in one round of blocks, at most 8
+        and at most one per tile (a captured graph plans from its fixed context length)."""
+        key = f"sink_attention/mma/splits/h{self.n_heads}w{self.window or 0}s{self.keep_first}"
+        if key not in ctx.scratch:
+            from paged_kv_serving_b200.parts.attention import _sm_count
+
+            splits = 1
+            if max(ctx.seq_lens) <= 4:
+                longest = max(f + n for f, n in zip(ctx.first_positions, ctx.seq_lens))
+                if ctx.planning_context_len is not None:
+                    longest = ctx.planning_context_len
+                if self.window:
+                    longest = min(longest, self.window + self.keep_first + 64)
+                tiles = max(1, -(-longest // 64))
+                blocks = len(ctx.seq_lens) * self.n_heads
+                splits = int(max(1, min(8, tiles, (4 * _sm_count(ctx.device)) // max(blocks, 1))))      # about four blocks fit an SM
+            ctx.scratch[key] = splits
+        return ctx.scratch[key]
+
     def _plan_mma(self, ctx: StepContext) -> None:
         seq_name, q0_name = "sink_attention/mma/work_seq", "sink_attention/mma/work_q0"
+        self._mma_splits(ctx)
         if seq_name in ctx.arena:
             return
         rows = mixer_ops.attention_sink_mma_rows()
@@ -256,7 +279,8 @@ class SinkWindowAttention(Part):
             attended = mixer_ops.attention_sink_mma(
                 qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
                 ctx.ints("sink_attention/mma/work_seq"), ctx.ints("sink_attention/mma/work_q0"), self.n_heads, self.n_kv_heads,
-                self.dim, self.vdim, group.page_size, self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status)
+                self.dim, self.vdim, group.page_size, self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status,
+                num_splits=self._mma_splits(ctx))
             return gemm.linear(attended, self.o, out_dtype=torch.float32, few_rows_f32=True, chain=True)
         seq_name, row_name = self._work_names()
         attended = mixer_ops.attention_sink(
