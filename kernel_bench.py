@@ -273,11 +273,11 @@ def bench_sink_attention(config, page: int) -> None:
                     forms.append(("TMA decode", lambda i: ops.attention_decode_tma(
                         qkv, out, k[i % layers], v[i % layers], table, starts, first, entries, 1, h, kv, dk, page, window, scale, 8,
                         status, False, keep_first=keep, softcap=cap)))
-            seq, q0 = lists(queries, batch, mixer_ops.attention_sink_mma_rows())
-            splits = 1 if queries > 1 else 4
+            splits = 1 if queries > 1 else 8
+            mseq, mrow = lists(queries * (h // kv), batch, mixer_ops.attention_sink_mma_rows())
             forms.append(("mma.sync", lambda i: mixer_ops.attention_sink_mma(
-                qkv, k[i % layers], v[i % layers], table, starts, first, seq, q0, h, kv, dk, dv, page, window, keep, scale, cap, status,
-                num_splits=splits)))
+                qkv, k[i % layers], v[i % layers], table, starts, first, mseq, mrow, h, kv, dk, dv, page, window, keep, scale, cap,
+                status, num_splits=splits)))
             rows = mixer_ops.attention_sink_rows_per_block()
             group_rows = queries * (h // kv)
             blocks = -(-group_rows // rows)

@@ -239,14 +239,16 @@ attention_sink_kernel(const A* __restrict__ q, A* __restrict__ out, const C* __r
 
 // --- attention on tensor cores (bfloat16, head sizes that are multiples of 16) -----------------------
 //
-// One block of 4 warps per (64 query rows of one entry, query head); each warp owns 16 rows. Keys
+// The rows of one (entry, key/value head) are (query token, head in group) pairs, row = token *
+// group + head in group, so that all query heads of a key/value head share its tiles. One block of
+// 4 warps per 64 consecutive rows; each warp owns 16 rows. Keys
 // and values are walked in tiles of 64 absolute positions, aligned to multiples of 64 from position
 // 0 (first the tiles that hold kept first tokens, then the window's; one range where they meet),
 // double-buffered with cp.async from the pages the block table names. Both products run on
 // mma.sync m16n8k16 (bfloat16 operands, float32 accumulators); scores, cap, mask, maxima, sums and
 // the output accumulator are float32. The key size is a run-time number (it only sets the number
 // of k-steps of the first product); the value size is a template parameter (it sizes the
-// accumulator). Entries of a few rows (decode) take the same kernel, one block per entry and head;
+// accumulator). Entries of a few rows (decode) take the same kernel, one block per entry and key/value head;
 // for steps that hold nothing else the tile list of every block is cut into up to 8 shares that run
 // side by side (blockIdx.z) and a second kernel merges their (maximum, sum, accumulator) states.
 
@@ -329,18 +331,22 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
   bf16* k_s = q_s + SM_BM * ldk;                       // [2][64][ldk]
   bf16* v_s = k_s + 2 * SM_BN * ldk;                   // [2][64][LDV]
 
-  const int s = p.work_seq[blockIdx.x], q0 = p.work_q0[blockIdx.x];
-  const int head = blockIdx.y;
-  const int kvh = head / (p.n_heads / p.n_kv);
+  const int s = p.work_seq[blockIdx.x], row0 = p.work_q0[blockIdx.x];
+  const int kvh = blockIdx.y;
+  const int group = p.n_heads / p.n_kv;
   const int tok0 = p.seq_starts[s];
   const int n_q = p.seq_starts[s + 1] - tok0;
   const int pos0 = p.first_pos[s];
-  const int rows_valid = min(SM_BM, n_q - q0);
+  const int rows_valid = min(SM_BM, n_q * group - row0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
+  // token (in the step), query head and position of a row of this block
+  auto tok_of = [=](int r) { return tok0 + (row0 + r) / group; };
+  auto head_of = [=](int r) { return kvh * group + (row0 + r) % group; };
+  auto qpos_of = [=](int r) { return pos0 + (row0 + r) / group; };
 
-  const int qpos_first = pos0 + q0;
-  const int key_hi = qpos_first + rows_valid;                                   // exclusive
+  const int qpos_first = qpos_of(0);
+  const int key_hi = qpos_of(rows_valid - 1) + 1;                               // exclusive
   const int key_lo = p.window > 0 ? max(0, qpos_first - p.window + 1) : 0;
   const int keep = p.window > 0 ? min(p.keep_first, key_hi) : 0;
   const int tile_end = (key_hi - 1) / SM_BN;
@@ -358,7 +364,7 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
   const int j_begin = blockIdx.z * per_split, j_end = min(listed, j_begin + per_split);
   if (j_begin >= j_end) {               // (only with splits) nothing to do: an empty state
     for (int idx = threadIdx.x; idx < rows_valid; idx += SM_THREADS) {
-      const size_t at = ((size_t)(tok0 + q0 + idx) * p.n_heads + head) * p.num_splits + blockIdx.z;
+      const size_t at = ((size_t)tok_of(idx) * p.n_heads + head_of(idx)) * p.num_splits + blockIdx.z;
       p.part_ml[2 * at] = -INFINITY;
       p.part_ml[2 * at + 1] = 0.0f;
       for (int d = 0; d < DV; ++d) p.part_o[at * DV + d] = 0.0f;
@@ -370,7 +376,7 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
     const int row = idx / (dk >> 3), chunk = idx - row * (dk >> 3);
     bf16* dst = q_s + row * ldk + chunk * 8;
     if (row < rows_valid)
-      sm_cp16(dst, p.q + (size_t)(tok0 + q0 + row) * p.q_ld + (size_t)head * dk + chunk * 8);
+      sm_cp16(dst, p.q + (size_t)tok_of(row) * p.q_ld + (size_t)head_of(row) * dk + chunk * 8);
     else
       *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
   }
@@ -379,9 +385,9 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
   sm_commit();
 
   const int row_a = warp * 16 + g, row_b = row_a + 8;
-  const int qpos_a = qpos_first + row_a, qpos_b = qpos_first + row_b;
-  const int warp_qpos_min = qpos_first + warp * 16;
-  const int warp_qpos_max = min(qpos_first + warp * 16 + 15, key_hi - 1);
+  const int qpos_a = qpos_of(row_a), qpos_b = qpos_of(row_b);
+  const int warp_qpos_min = qpos_of(warp * 16);
+  const int warp_qpos_max = min(qpos_of(warp * 16 + 15), key_hi - 1);
   const bool warp_active = warp * 16 < rows_valid;
 
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
@@ -486,13 +492,13 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
   if (p.num_splits > 1) {
     // this share's state: the merge kernel folds the shares of a row in ascending order
     if (row_a < rows_valid) {
-      const size_t at = ((size_t)(tok0 + q0 + row_a) * p.n_heads + head) * p.num_splits + blockIdx.z;
+      const size_t at = ((size_t)tok_of(row_a) * p.n_heads + head_of(row_a)) * p.num_splits + blockIdx.z;
       if (t4 == 0) { p.part_ml[2 * at] = m_a; p.part_ml[2 * at + 1] = l_a; }
 #pragma unroll
       for (int i = 0; i < DTILES; ++i) { p.part_o[at * DV + i * 8 + 2 * t4] = o[i][0]; p.part_o[at * DV + i * 8 + 2 * t4 + 1] = o[i][1]; }
     }
     if (row_b < rows_valid) {
-      const size_t at = ((size_t)(tok0 + q0 + row_b) * p.n_heads + head) * p.num_splits + blockIdx.z;
+      const size_t at = ((size_t)tok_of(row_b) * p.n_heads + head_of(row_b)) * p.num_splits + blockIdx.z;
       if (t4 == 0) { p.part_ml[2 * at] = m_b; p.part_ml[2 * at + 1] = l_b; }
 #pragma unroll
       for (int i = 0; i < DTILES; ++i) { p.part_o[at * DV + i * 8 + 2 * t4] = o[i][2]; p.part_o[at * DV + i * 8 + 2 * t4 + 1] = o[i][3]; }
@@ -502,12 +508,12 @@ __global__ void __launch_bounds__(SM_THREADS) attention_sink_mma_kernel(const Si
   const float inv_a = l_a > 0.0f ? 1.0f / l_a : 0.0f, inv_b = l_b > 0.0f ? 1.0f / l_b : 0.0f;
   const size_t out_stride = (size_t)p.n_heads * DV;
   if (row_a < rows_valid) {
-    bf16* dst = p.out + (size_t)(tok0 + q0 + row_a) * out_stride + (size_t)head * DV;
+    bf16* dst = p.out + (size_t)tok_of(row_a) * out_stride + (size_t)head_of(row_a) * DV;
 #pragma unroll
     for (int i = 0; i < DTILES; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = sm_pack(o[i][0] * inv_a, o[i][1] * inv_a);
   }
   if (row_b < rows_valid) {
-    bf16* dst = p.out + (size_t)(tok0 + q0 + row_b) * out_stride + (size_t)head * DV;
+    bf16* dst = p.out + (size_t)tok_of(row_b) * out_stride + (size_t)head_of(row_b) * DV;
 #pragma unroll
     for (int i = 0; i < DTILES; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = sm_pack(o[i][2] * inv_b, o[i][3] * inv_b);
   }
@@ -624,7 +630,7 @@ static int launch_sink_mma(const SinkMmaParams& p, int n_work, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(attention_sink_mma_kernel<DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  const int rc = launch_kernel(attention_sink_mma_kernel<DV>, dim3(n_work, p.n_heads, p.num_splits), dim3(SM_THREADS), smem, s,
+  const int rc = launch_kernel(attention_sink_mma_kernel<DV>, dim3(n_work, p.n_kv, p.num_splits), dim3(SM_THREADS), smem, s,
                                true, 0, p);
   return rc;
 }
@@ -637,7 +643,8 @@ PKV_EXPORT int pkv_attention_sink_mma_supports(int dk, int dv, int q_ld) {
 
 PKV_EXPORT int pkv_attention_sink_mma_rows() { return SM_BM; }
 
-// The work list is in blocks of 64 query rows of an entry (work_q0: the block's first query).
+// The work list is in blocks of 64 rows of an (entry, key/value head): row = token * (H / G) + head in
+// group; work_q0 is the block's first row.
 PKV_EXPORT int pkv_attention_sink_mma(const void* q, int q_ld, void* out, const void* k_pool, const void* v_pool,
                                       const int32_t* block_table, int table_stride, const int32_t* seq_starts,
                                       const int32_t* first_pos, const int32_t* work_seq, const int32_t* work_q0, int n_work,
@@ -648,7 +655,7 @@ PKV_EXPORT int pkv_attention_sink_mma(const void* q, int q_ld, void* out, const 
   if (!pkv_attention_sink_mma_supports(dk, dv, q_ld)) return PKV_ERR_LIMIT;
   if (num_splits < 1 || num_splits > 8 || (num_splits > 1 && (!part_o || !part_ml))) return PKV_ERR_SIZE;
   if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size <= 0 || window < 0 || keep_first < 0 || num_pages <= 0 ||
-      softcap < 0.0f || !(scale > 0.0f) || n_heads > 65535)
+      softcap < 0.0f || !(scale > 0.0f) || n_kv > 65535)
     return PKV_ERR_SIZE;
   if ((uintptr_t)q % 16 || (uintptr_t)k_pool % 16 || (uintptr_t)v_pool % 16 || (uintptr_t)out % 4) return PKV_ERR_ALIGN;
   const float log2e = 1.4426950408889634f;

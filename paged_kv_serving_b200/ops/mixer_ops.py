@@ -504,7 +504,7 @@ def attention_sink_mma_supports(dim: int, vdim: int, q_row_stride: int) -> bool:
 
 
 def attention_sink_mma_rows() -> int:
-    """Query rows of one work item of ``attention_sink_mma``."""
+    """Rows of one work item of ``attention_sink_mma``."""
     return 64
 
 
@@ -513,9 +513,10 @@ def attention_sink_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
                        n_heads: int, n_kv: int, dim: int, vdim: int, page_size: int, window: int, keep_first: int, scale: float,
                        softcap: float, status: torch.Tensor, num_splits: int = 1) -> torch.Tensor:
     """``attention_sink`` on the tensor cores (``mma.sync``, bfloat16 operands, float32 scores and
-    accumulators) for head sizes that are multiples of 16. The work list is in blocks of
-    ``attention_sink_mma_rows()`` queries of an entry (``work_q0``: the block's first query) and
-    must cover every token of the step when ``num_splits`` > 1: every block's key range is then
+    accumulators) for head sizes that are multiples of 16. The rows of an (entry, key/value head)
+    are (token, head in group) pairs, ``row = token * (H / G) + head in group``; the work list is in
+    blocks of ``attention_sink_mma_rows()`` rows (``work_q0``: the block's first row) and must
+    cover every token of the step when ``num_splits`` > 1: every block's key range is then
     cut into that many shares (at most 8) that run side by side and are merged by a second
     kernel (for steps of few rows over long contexts)."""
     _need(q, torch.bfloat16, "q"); _need(k_pool, torch.bfloat16, "k_pool"); _need(v_pool, torch.bfloat16, "v_pool")

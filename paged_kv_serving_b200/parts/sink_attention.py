@@ -147,12 +147,15 @@ class SinkWindowAttention(Part):
         return (self.USE_TENSOR_CORES and ctx.dtype == torch.bfloat16
                 and mixer_ops.attention_sink_mma_supports(self.dim, self.vdim, self.fused_rows))
 
+    def _mma_names(self) -> tuple[str, str]:
+        return (f"sink_attention/mma/work_seq/g{self.group_size}", f"sink_attention/mma/work_row0/g{self.group_size}")
+
     def _mma_splits(self, ctx: StepContext) -> int:
         """Shares of the key range per block of the ``mma.sync`` kernel: one, unless the step holds
         only entries of a few tokens over long contexts (decode steps), whose few blocks would
         each walk their tiles in a row; then as many as still run in one round of blocks, at most 8
         and at most one per tile (a captured graph plans from its fixed context length)."""
-        key = f"sink_attention/mma/splits/h{self.n_heads}w{self.window or 0}s{self.keep_first}"
+        key = f"sink_attention/mma/splits/k{self.n_kv_heads}w{self.window or 0}s{self.keep_first}"
         if key not in ctx.scratch:
             from paged_kv_serving_b200.parts.attention import _sm_count
 
@@ -164,24 +167,24 @@ class SinkWindowAttention(Part):
                 if self.window:
                     longest = min(longest, self.window + self.keep_first + 64)
                 tiles = max(1, -(-longest // 64))
-                blocks = len(ctx.seq_lens) * self.n_heads
+                blocks = len(ctx.seq_lens) * self.n_kv_heads
                 splits = int(max(1, min(8, tiles, (4 * _sm_count(ctx.device)) // max(blocks, 1))))      # about four blocks fit an SM
             ctx.scratch[key] = splits
         return ctx.scratch[key]
 
     def _plan_mma(self, ctx: StepContext) -> None:
-        seq_name, q0_name = "sink_attention/mma/work_seq", "sink_attention/mma/work_q0"
+        seq_name, q0_name = self._mma_names()
         self._mma_splits(ctx)
         if seq_name in ctx.arena:
             return
         rows = mixer_ops.attention_sink_mma_rows()
-        lens = np.asarray(ctx.seq_lens, dtype=np.int64)
+        lens = np.asarray(ctx.seq_lens, dtype=np.int64) * self.group_size     # rows of an (entry, key/value head)
         first = np.asarray(ctx.first_positions, dtype=np.int64)
         blocks = (lens + rows - 1) // rows
         work_seq = np.repeat(np.arange(len(lens), dtype=np.int64), blocks)
         starts = np.cumsum(blocks) - blocks
         work_q0 = (np.arange(int(blocks.sum()), dtype=np.int64) - np.repeat(starts, blocks)) * rows
-        order = np.argsort(-(first[work_seq] + work_q0), kind="stable")       # the longest key ranges first
+        order = np.argsort(-(first[work_seq] + work_q0 // self.group_size), kind="stable")      # the longest key ranges first
         ctx.arena.add(seq_name, work_seq[order])
         ctx.arena.add(q0_name, work_q0[order])
 
@@ -278,7 +281,7 @@ class SinkWindowAttention(Part):
         if self._mma(ctx):
             attended = mixer_ops.attention_sink_mma(
                 qkv, k_pool, v_pool, ctx.ints(group.table_name), ctx.ints(ctx.SEQ_STARTS), ctx.ints(ctx.FIRST_POS),
-                ctx.ints("sink_attention/mma/work_seq"), ctx.ints("sink_attention/mma/work_q0"), self.n_heads, self.n_kv_heads,
+                ctx.ints(self._mma_names()[0]), ctx.ints(self._mma_names()[1]), self.n_heads, self.n_kv_heads,
                 self.dim, self.vdim, group.page_size, self.window or 0, self.keep_first, self.scale, self.softcap, ctx.status,
                 num_splits=self._mma_splits(ctx))
             return gemm.linear(attended, self.o, out_dtype=torch.float32, few_rows_f32=True, chain=True)
