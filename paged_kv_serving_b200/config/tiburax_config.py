@@ -16,10 +16,11 @@ __all__ = ["TiburaxConfig"]
 
 _TOP = {"architecture", "vocab", "width", "norm", "embedding", "layers", "max_positions"}
 _REQUIRED = {
-    "attention": {"heads", "kv_heads", "dim", "vdim", "scale", "mask", "rot"},
+    "attention": {"heads", "kv_heads", "dim", "vdim", "scale"},
     "mamba1": {"inner", "state", "dt_rank", "conv"},
 }
-_OPTIONAL = {"attention": {"softcap", "v_mix"}, "mamba1": set()}
+#: (no mask: every earlier position is visible; no rot: no rotation; no softcap: scores as they are)
+_OPTIONAL = {"attention": {"mask", "rot", "softcap", "v_mix"}, "mamba1": set()}
 #: Positions an engine may be asked for when the file sets no bound of its own: the rotation's
 #: angles are computed from the position, no table limits them.
 DEFAULT_MAX_POSITIONS = 1 << 20
@@ -68,12 +69,12 @@ class TiburaxConfig:
                     raise ValueError(f"layer {i}: heads must be a multiple of kv_heads")
                 dim = _positive_int(mixer["dim"], f"layer {i}: dim")
                 _positive_int(mixer["vdim"], f"layer {i}: vdim")
-                mask = mixer["mask"] or {}
+                mask = mixer.get("mask") or {}
                 if mask.get("size") is not None:
                     _positive_int(mask["size"], f"layer {i}: mask.size")
                 if int(mask.get("keep_first") or 0) < 0:
                     raise ValueError(f"layer {i}: mask.keep_first must be >= 0")
-                rot = mixer["rot"] or {}
+                rot = mixer.get("rot") or {}
                 dims = int(rot.get("dims") or 0)
                 if dims < 0 or dims % 2 or dims > dim:
                     raise ValueError(f"layer {i}: rot.dims must be even and at most dim")

@@ -87,8 +87,10 @@ def attention(h: torch.Tensor, p: dict, m: dict, eps: float, v_first: torch.Tens
     q = (h @ p["q"].to(F64).T).view(n, heads, dim)
     k = (h @ p["k"].to(F64).T).view(n, groups, dim)
     v = (h @ p["v"].to(F64).T).view(n, groups, vdim)
-    q = rms_unit(rotate(q, positions, m["rot"]), eps)
-    k = rms_unit(rotate(k, positions, m["rot"]), eps)
+    rot = m.get("rot") or {}
+    if int(rot.get("dims") or 0):
+        q, k = rotate(q, positions, rot), rotate(k, positions, rot)
+    q, k = rms_unit(q, eps), rms_unit(k, eps)
     if v_first is not None:
         lam = p["vmix"].to(F64)
         v = (1.0 - lam) * v + lam * v_first
@@ -98,7 +100,8 @@ def attention(h: torch.Tensor, p: dict, m: dict, eps: float, v_first: torch.Tens
     cap = float(m.get("softcap") or 0.0)
     if cap:
         score = cap * torch.tanh(score / cap)
-    mask = visible(n, int(m["mask"]["size"]), int(m["mask"]["keep_first"]))
+    window = (m.get("mask") or {}).get("size")
+    mask = visible(n, int(window) if window else n, int((m.get("mask") or {}).get("keep_first") or 0))
     score = score.masked_fill(~mask[None], float("-inf"))
     weight = torch.softmax(score, dim=-1)
     out = torch.einsum("hij,jhd->ihd", weight, v_of_head).reshape(n, heads * vdim)

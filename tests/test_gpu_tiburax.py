@@ -464,6 +464,13 @@ SINGLE = {
 }
 
 
+SINGLE["attention_without_mask_rotation_and_cap_keys"] = copy.deepcopy(SINGLE["attention_plain"])
+for _key in ("mask", "rot", "softcap", "v_mix"):
+    SINGLE["attention_without_mask_rotation_and_cap_keys"]["layers"][0]["mixer"].pop(_key)
+SINGLE["attention_with_null_mask"] = copy.deepcopy(SINGLE["attention_grouped_keys"])
+SINGLE["attention_with_null_mask"]["layers"][0]["mixer"]["mask"] = None
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("what", sorted(SINGLE))
 def test_each_mechanism_alone(what, dtype):

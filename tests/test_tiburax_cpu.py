@@ -82,6 +82,18 @@ def test_layout_names_roles_and_cache_requests():
     assert [m.value_share for m in mixers[1:]] == [None, "source", "blend"]
     assert isinstance(mixers[1], SinkWindowAttention) and mixers[1].rotary.scaling is None and mixers[2].rotary.scaling is not None
     assert mixers[3].softcap == 0.0 and mixers[3].keep_first == 0 and mixers[3].window == 5
+    bare = copy.deepcopy(CONFIG)
+    for key in ("mask", "rot"):
+        bare["layers"][3]["mixer"].pop(key)
+    bare["layers"][1]["mixer"]["mask"] = None
+    bare["layers"][2]["mixer"]["mask"] = {"size": None, "keep_first": 3}
+    bare["layers"][2]["mlp"]["shared"] = None
+    del bare["embedding"]
+    _, plain_layout = _layout(bare)
+    plain_mixers = [block.mixer for block in plain_layout.blocks]
+    assert plain_mixers[3].window is None and plain_mixers[3].rotary is None and plain_mixers[1].window is None
+    assert plain_mixers[2].window is None and plain_mixers[2].cache_request().keep_first == 0
+    assert plain_layout.blocks[2].feed_forward.shared_inner == 0 and plain_layout.embedding.scale == 1.0
     groups, states = plan_groups(layout.cache_entries())
     assert len(groups) == 2 and len(states) == 2
     by_dim = {g.head_dim: g for g in groups}
